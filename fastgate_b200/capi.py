@@ -1,0 +1,84 @@
+"""ctypes binding of the C ABI in include/fastgate_b200.h.
+
+This is the route for callers that do not want the pybind module (and the one the parity
+tests use): device pointers are passed as integers, e.g. ``tensor.data_ptr()``.
+There is no CPU fallback: if libfastgate_b200.so is missing the import fails.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfastgate_b200.so")
+
+FG_OK, FG_ERR_SHAPE, FG_ERR_ALIGN, FG_ERR_NULL, FG_ERR_WORKSPACE = 0, 1, 2, 3, 4
+FG_ERR_CUDA, FG_ERR_TIMEOUT, FG_ERR_PLAN, FG_ERR_NO_DEVICE = 5, 6, 7, 8
+FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK = 0, 1, 2
+
+# every symbol include/fastgate_b200.h declares
+EXPORTS = (
+    "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
+    "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_planned", "fg_linear_host",
+    "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
+)
+
+
+class Plan(ctypes.Structure):
+    """Mirror of fg_plan_t."""
+
+    _fields_ = [(n, ctypes.c_int) for n in (
+        "op", "m_tile", "k_per_stage", "stages", "consumer_warps", "grid", "tiles", "k_blocks",
+        "smem_bytes", "passes", "math")]
+
+    def as_dict(self) -> dict:
+        return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m fastgate_b200.build` "
+            "(fastgate_b200 has no CPU fallback)")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, sz, i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    L.fg_plan.argtypes = [i, i, i, i, i, i, ctypes.POINTER(Plan)]
+    L.fg_plan_validate.argtypes = [ctypes.POINTER(Plan), i, i, i]
+    L.fg_workspace_bytes.argtypes = [i]
+    L.fg_workspace_bytes.restype = sz
+    L.fg_workspace_init.argtypes = [vp, sz, vp]
+    L.fg_workspace_status.argtypes = [vp, ctypes.POINTER(i), vp]
+    L.fg_gemm_f16_kn.argtypes = [vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_gemm_f16_nk.argtypes = [vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_gemm_w8a16_nk.argtypes = [vp, vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_gemm_planned.argtypes = [ctypes.POINTER(Plan), vp, vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_status_str.argtypes = [i]
+    L.fg_status_str.restype = ctypes.c_char_p
+    L.fg_last_cuda_error.restype = i
+    L.fg_launch_count.restype = ctypes.c_ulonglong
+    L.fg_version.restype = ctypes.c_char_p
+    return L
+
+
+lib = _load()
+
+
+def status_str(st: int) -> str:
+    return lib.fg_status_str(st).decode()
+
+
+def plan(op: int, M: int, N: int, K: int, sm_count: int = 0, smem_optin: int = 0) -> Plan:
+    p = Plan()
+    st = lib.fg_plan(op, M, N, K, sm_count, smem_optin, ctypes.byref(p))
+    if st != FG_OK:
+        raise ValueError(status_str(st))
+    return p
+
+
+def workspace_bytes(N: int) -> int:
+    return int(lib.fg_workspace_bytes(N))
+
+
+def launch_count() -> int:
+    return int(lib.fg_launch_count())

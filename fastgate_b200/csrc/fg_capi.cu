@@ -1,0 +1,312 @@
+// C ABI of fastgate_b200: argument checks, tensor-map encoding, kernel launch.
+// Host code only depends on the CUDA runtime; the driver's tensor-map encoder is
+// looked up at run time, so the library loads (and fg_plan works) on a box without a GPU.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/fastgate_b200.h"
+#include "fg_kernels.cuh"
+#include "fg_layout.h"
+
+static_assert(FG_TILE_N == fg::kTileN, "layout mismatch");
+static_assert(FG_RED_STRIDE == fg::kRedStride, "layout mismatch");
+static_assert(FG_CHUNK_W_BYTES == fg::kChunkWBytes, "layout mismatch");
+static_assert(FG_MAX_CONSUMER_WARPS == fg::kMaxConsumerWarps, "layout mismatch");
+static_assert(int(FG_ERR_TIMEOUT) == int(fg::kStatusTimeout), "status mismatch");
+static_assert(int(FG_OP_F16_KN) == int(fg::kOpF16KN) && int(FG_OP_F16_NK) == int(fg::kOpF16NK) &&
+                  int(FG_OP_W8A16_NK) == int(fg::kOpW8A16NK),
+              "op code mismatch");
+
+extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin_bytes);
+
+namespace {
+
+thread_local int g_last_cuda = 0;
+std::atomic<unsigned long long> g_launches{0};
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int smem_optin = 0;
+  int cc_major = 0;
+  int smem_set[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
+};
+
+constexpr int kMaxDevices = 64;
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_dev_mu;
+
+int device_info(DeviceInfo** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_NO_DEVICE;
+  }
+  if (dev < 0 || dev >= kMaxDevices) return FG_ERR_NO_DEVICE;
+  DeviceInfo& d = g_dev[dev];
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (d.sm_count == 0) {
+    int sm = 0, optin = 0, major = 0;
+    if ((e = cudaDeviceGetAttribute(&sm, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    d.smem_optin = optin;
+    d.cc_major = major;
+    d.sm_count = sm;
+  }
+  if (d.cc_major != 10) return FG_ERR_NO_DEVICE;  // the kernels are sm_100a only
+  *out = &d;
+  return FG_OK;
+}
+
+// 2-D row-major tensor: `inner` contiguous elements per row, `rows` rows, 128B swizzle.
+int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base,
+              uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encoder();
+  if (enc == nullptr) return FG_ERR_CUDA;
+  const cuuint64_t gdim[2] = {inner, rows};
+  const cuuint64_t gstride[1] = {inner * static_cast<uint64_t>(elem_bytes)};
+  const cuuint32_t box[2] = {box_inner, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(tm, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    g_last_cuda = static_cast<int>(r);
+    return FG_ERR_CUDA;
+  }
+  return FG_OK;
+}
+
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const fg::KParams);
+
+KernelFn pick_kernel(int op, int m_tile) {
+  switch (op * 2 + (m_tile == 16)) {
+    case 0: return fg::fg_streamk_kernel<fg::kOpF16KN, 8>;
+    case 1: return fg::fg_streamk_kernel<fg::kOpF16KN, 16>;
+    case 2: return fg::fg_streamk_kernel<fg::kOpF16NK, 8>;
+    case 3: return fg::fg_streamk_kernel<fg::kOpF16NK, 16>;
+    case 4: return fg::fg_streamk_kernel<fg::kOpW8A16NK, 8>;
+    default: return fg::fg_streamk_kernel<fg::kOpW8A16NK, 16>;
+  }
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_common(const void* x, const void* W, const void* C, int M, int N, int K, void* ws,
+                 size_t ws_bytes) {
+  if (x == nullptr || W == nullptr || C == nullptr) return FG_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || (N % 128) != 0 || (K % 128) != 0) return FG_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(W) || !aligned16(C)) return FG_ERR_ALIGN;
+  if (ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return FG_ERR_WORKSPACE;
+  if (ws_bytes < FG_WS_TICKETS_OFFSET + 4 * static_cast<size_t>(N / 128)) return FG_ERR_WORKSPACE;
+  return FG_OK;
+}
+
+int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
+                const void* scales, void* C, int M, int N, int K, void* ws, cudaStream_t stream) {
+  const int op = pl.op;
+  const int chunks = pl.k_per_stage / fg_chunk_k(op);
+  KernelFn kern = pick_kernel(op, pl.m_tile);
+  int& set = dev->smem_set[op][pl.m_tile == 16];
+  if (pl.smem_bytes > set) {
+    const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
+    if (e != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    set = pl.smem_bytes;
+  }
+
+  CUtensorMap tmW;
+  int st;
+  if (op == FG_OP_F16_KN)
+    st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, W, N, K, 64, 64);
+  else if (op == FG_OP_F16_NK)
+    st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, W, K, N, 64, 128);
+  else
+    st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, K, N, 128, 128);
+  if (st != FG_OK) return st;
+
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  fg::KParams p;
+  p.scales = static_cast<const __half*>(scales);
+  p.partials = reinterpret_cast<float*>(wsb + FG_WS_HEADER_BYTES);
+  p.tickets = reinterpret_cast<unsigned int*>(wsb + FG_WS_TICKETS_OFFSET);
+  p.status = reinterpret_cast<int*>(wsb);
+  p.N = N;
+  p.K = K;
+  p.tiles = pl.tiles;
+  p.k_blocks = pl.k_blocks;
+  p.chunks_per_stage = chunks;
+  p.stages = pl.stages;
+  p.consumer_warps = pl.consumer_warps;
+
+  for (int m0 = 0; m0 < M; m0 += 16) {
+    const int mp = (M - m0) < 16 ? (M - m0) : 16;
+    if (mp > pl.m_tile) return FG_ERR_PLAN;
+    const __half* xp = static_cast<const __half*>(x) + static_cast<size_t>(m0) * K;
+    CUtensorMap tmX;
+    st = encode_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xp, K, mp, 64, pl.m_tile);
+    if (st != FG_OK) return st;
+    p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * N;
+    p.M = mp;
+    kern<<<pl.grid, (pl.consumer_warps + 1) * 32, pl.smem_bytes, stream>>>(tmW, tmX, p);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
+  return FG_OK;
+}
+
+int run_op(int op, const void* x, const void* W, const void* scales, void* C, int M, int N, int K,
+           void* ws, size_t ws_bytes, fg_stream_t stream) {
+  int st = check_common(x, W, C, M, N, K, ws, ws_bytes);
+  if (st != FG_OK) return st;
+  if (scales != nullptr && (reinterpret_cast<uintptr_t>(scales) & 3u) != 0) return FG_ERR_ALIGN;
+  DeviceInfo* dev = nullptr;
+  if ((st = device_info(&dev)) != FG_OK) return st;
+  fg_plan_t pl;
+  if ((st = fg_plan(op, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+  return run_planned(pl, dev, x, W, scales, C, M, N, K, ws, reinterpret_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t fg_workspace_bytes(int N) {
+  const size_t tiles = N > 0 ? static_cast<size_t>((N + 127) / 128) : 0;
+  return FG_WS_TICKETS_OFFSET + ((4 * tiles + 255) / 256) * 256;
+}
+
+int fg_workspace_init(void* ws, size_t ws_bytes, fg_stream_t stream) {
+  if (ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0 || ws_bytes < FG_WS_TICKETS_OFFSET)
+    return FG_ERR_WORKSPACE;
+  const cudaError_t e = cudaMemsetAsync(ws, 0, ws_bytes, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  return FG_OK;
+}
+
+int fg_workspace_status(void* ws, int* status_out, fg_stream_t stream) {
+  if (ws == nullptr || status_out == nullptr) return FG_ERR_NULL;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int v = 0;
+  cudaError_t e = cudaMemcpyAsync(&v, ws, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess && v != 0) e = cudaMemsetAsync(ws, 0, sizeof(int), s);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  *status_out = v;
+  return FG_OK;
+}
+
+int fg_gemm_f16_kn(const void* A, const void* B, void* C, int M, int N, int K, void* ws,
+                   size_t ws_bytes, fg_stream_t stream) {
+  return run_op(FG_OP_F16_KN, A, B, nullptr, C, M, N, K, ws, ws_bytes, stream);
+}
+
+int fg_gemm_f16_nk(const void* x, const void* W, void* C, int M, int N, int K, void* ws,
+                   size_t ws_bytes, fg_stream_t stream) {
+  return run_op(FG_OP_F16_NK, x, W, nullptr, C, M, N, K, ws, ws_bytes, stream);
+}
+
+int fg_gemm_w8a16_nk(const void* x, const int8_t* W8, const void* scales, void* C, int M, int N,
+                     int K, void* ws, size_t ws_bytes, fg_stream_t stream) {
+  return run_op(FG_OP_W8A16_NK, x, W8, scales, C, M, N, K, ws, ws_bytes, stream);
+}
+
+int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const void* scales, void* C,
+                    int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream) {
+  if (plan == nullptr) return FG_ERR_NULL;
+  int st = check_common(x, W, C, M, N, K, ws, ws_bytes);
+  if (st != FG_OK) return st;
+  DeviceInfo* dev = nullptr;
+  if ((st = device_info(&dev)) != FG_OK) return st;
+  if ((st = fg_plan_validate(plan, N, K, dev->smem_optin)) != FG_OK) return st;
+  if (plan->passes != (M + 15) / 16) return FG_ERR_PLAN;
+  return run_planned(*plan, dev, x, W, plan->op == FG_OP_W8A16_NK ? scales : nullptr, C, M, N, K, ws,
+                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev, void* C_host,
+                   void* x_stage_dev, void* C_stage_dev, int M, int N, int K, void* ws,
+                   size_t ws_bytes, fg_stream_t stream) {
+  if (x_host == nullptr || C_host == nullptr || x_stage_dev == nullptr || C_stage_dev == nullptr)
+    return FG_ERR_NULL;
+  if (op < FG_OP_F16_KN || op > FG_OP_W8A16_NK) return FG_ERR_PLAN;
+  if (M <= 0 || N <= 0 || K <= 0) return FG_ERR_SHAPE;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyAsync(x_stage_dev, x_host, static_cast<size_t>(M) * K * 2,
+                                  cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  const int st = run_op(op, x_stage_dev, W_dev, op == FG_OP_W8A16_NK ? scales_dev : nullptr,
+                        C_stage_dev, M, N, K, ws, ws_bytes, stream);
+  if (st != FG_OK) return st;
+  e = cudaMemcpyAsync(C_host, C_stage_dev, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  return FG_OK;
+}
+
+const char* fg_status_str(int status) {
+  switch (status) {
+    case FG_OK: return "ok";
+    case FG_ERR_SHAPE: return "K(input column) & N(output column) must be multiple of 128!";
+    case FG_ERR_ALIGN: return "pointer is not 16-byte aligned";
+    case FG_ERR_NULL: return "required pointer is NULL";
+    case FG_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+    case FG_ERR_CUDA: return "CUDA call failed";
+    case FG_ERR_TIMEOUT: return "bounded device-side wait gave up";
+    case FG_ERR_PLAN: return "plan is not launchable";
+    case FG_ERR_NO_DEVICE: return "no sm_100 device is current";
+    default: return "unknown status";
+  }
+}
+
+int fg_last_cuda_error(void) { return g_last_cuda; }
+unsigned long long fg_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+const char* fg_version(void) { return "fastgate_b200 0.1 sm_100a"; }
+
+}  // extern "C"

@@ -1,0 +1,33 @@
+// Sizes shared by the host-side planner and the device kernel: how a pipeline stage,
+// the shared-memory carve-up and the workspace are laid out.
+#pragma once
+#include <stddef.h>
+
+#define FG_MAX_GRID 256            /* persistent CTAs the workspace has room for        */
+#define FG_MAX_STAGES 24           /* ring depth limit                                  */
+#define FG_MAX_CONSUMER_WARPS 8
+#define FG_TILE_N 128              /* output columns per tile                           */
+#define FG_CHUNK_W_BYTES 16384     /* weight bytes per chunk                            */
+#define FG_RED_STRIDE 132          /* floats per row of the cross-warp reduction buffer */
+
+/* Workspace: [0,256) status word; then FG_MAX_GRID x 2 partial tiles of 16 x 128 fp32;
+ * then one 32-bit arrival counter per output tile. */
+#define FG_WS_HEADER_BYTES 256
+#define FG_WS_PARTIAL_TILE_BYTES (16 * FG_TILE_N * 4)
+#define FG_WS_PARTIALS_BYTES ((size_t)FG_MAX_GRID * 2 * FG_WS_PARTIAL_TILE_BYTES)
+#define FG_WS_TICKETS_OFFSET (FG_WS_HEADER_BYTES + FG_WS_PARTIALS_BYTES)
+
+/* op codes mirror FG_OP_* of the public header */
+static inline int fg_chunk_k(int op) { return op == 2 ? 128 : 64; }
+/* activation boxes (64 k x m_tile rows, 128 B per row) that accompany one weight chunk */
+static inline int fg_x_boxes(int op) { return op == 2 ? 2 : 1; }
+static inline int fg_chunk_bytes(int op, int m_tile) {
+  return FG_CHUNK_W_BYTES + fg_x_boxes(op) * m_tile * 128;
+}
+/* reduction buffer + 1 KB alignment slack + flag word (the barriers are counted per stage) */
+static inline int fg_fixed_smem_bytes(int consumer_warps, int m_tile) {
+  return 1024 + consumer_warps * m_tile * FG_RED_STRIDE * 4 + 16;
+}
+static inline int fg_smem_bytes(int op, int m_tile, int chunks, int stages, int consumer_warps) {
+  return fg_fixed_smem_bytes(consumer_warps, m_tile) + stages * (chunks * fg_chunk_bytes(op, m_tile) + 16);
+}

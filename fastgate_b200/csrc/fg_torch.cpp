@@ -1,0 +1,164 @@
+// pybind11 / torch-extension surface of fastgate_b200.
+//
+// Same operator names, positional argument order and in-place-output convention as the
+// reference's host launchers (chanzhennan/Fastgate: backend/cuda/hk/edgemm.h:4-14,
+// edgemm_tr.h:7-11, flatgemm.h:4-10, fastgemv.h:4-7, backend/cuda/czn/fastgemm.h:4; bound
+// the way backend/pybind.cpp:21-27 binds free functions taking at::Tensor by value).
+// Every op is a thin layer over the C ABI (include/fastgate_b200.h): it validates the
+// tensors, picks the current CUDA stream and a cached per-(device, stream) workspace, and
+// turns status codes into exceptions.  There is no CPU path.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <utility>
+
+#include "../../include/fastgate_b200.h"
+
+namespace {
+
+struct Workspace {
+  at::Tensor buf;
+  size_t bytes = 0;
+};
+std::mutex g_ws_mu;
+std::map<std::pair<int, int64_t>, Workspace> g_ws;
+
+// One workspace per (device, stream): calls on one stream are ordered, calls on different
+// streams may overlap and must not share partial tiles or arrival counters.
+Workspace& workspace_for(int device, cudaStream_t stream, int N) {
+  const size_t need = fg_workspace_bytes(N);
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  Workspace& w = g_ws[{device, reinterpret_cast<int64_t>(stream)}];
+  if (w.bytes < need) {
+    const size_t bytes = std::max<size_t>(need, fg_workspace_bytes(65536));
+    w.buf = at::empty({static_cast<int64_t>(bytes)},
+                      at::TensorOptions().dtype(at::kByte).device(at::kCUDA, device));
+    const int st = fg_workspace_init(w.buf.data_ptr(), bytes, reinterpret_cast<fg_stream_t>(stream));
+    if (st != FG_OK) throw std::runtime_error(std::string("fastgate_b200: ") + fg_status_str(st));
+    w.bytes = bytes;
+  }
+  return w;
+}
+
+void check_tensor(const at::Tensor& t, const char* name, at::ScalarType dt) {
+  if (!t.is_cuda()) throw std::runtime_error(std::string("fastgate_b200: ") + name + " must be a CUDA tensor (there is no CPU path)");
+  if (t.scalar_type() != dt) throw std::runtime_error(std::string("fastgate_b200: ") + name + " has the wrong dtype");
+  if (!t.is_contiguous()) throw std::runtime_error(std::string("fastgate_b200: ") + name + " must be contiguous");
+}
+
+[[noreturn]] void raise(int st, bool transposed_weight) {
+  if (st == FG_ERR_SHAPE) {
+    // texts of backend/cuda/hk/edgemm.cu:108 and :280
+    throw std::invalid_argument(transposed_weight
+                                    ? "K(input column) & N(transposed output row) must be multiple of 128!"
+                                    : "K(input column) & N(output column) must be multiple of 128!");
+  }
+  throw std::runtime_error(std::string("fastgate_b200: ") + fg_status_str(st) + " (cuda error " +
+                           std::to_string(fg_last_cuda_error()) + ")");
+}
+
+// x[M,K] (fp16), weight in the given layout, C with M*N elements (fp16), scales[N] or undefined.
+void linear(int op, const at::Tensor& x, const at::Tensor& W, at::Tensor& C, const c10::optional<at::Tensor>& scales) {
+  check_tensor(x, "activation", at::kHalf);
+  check_tensor(W, "weight", op == FG_OP_W8A16_NK ? at::kChar : at::kHalf);
+  check_tensor(C, "output", at::kHalf);
+  if (x.dim() != 2 || W.dim() != 2) throw std::runtime_error("fastgate_b200: activation and weight must be 2-D");
+  const int64_t M = x.size(0), K = x.size(1);
+  const int64_t N = (op == FG_OP_F16_KN) ? W.size(1) : W.size(0);
+  const int64_t Kw = (op == FG_OP_F16_KN) ? W.size(0) : W.size(1);
+  if (Kw != K) throw std::runtime_error("fastgate_b200: activation and weight disagree on K");
+  if (C.numel() != M * N) throw std::runtime_error("fastgate_b200: output must hold M*N elements");
+  if (W.get_device() != x.get_device() || C.get_device() != x.get_device())
+    throw std::runtime_error("fastgate_b200: all tensors must live on one device");
+  const void* sp = nullptr;
+  if (scales.has_value() && scales->defined()) {
+    if (op != FG_OP_W8A16_NK) throw std::runtime_error("fastgate_b200: scales only apply to int8 weights");
+    check_tensor(*scales, "scales", at::kHalf);
+    if (scales->numel() != N) throw std::runtime_error("fastgate_b200: scales must hold N elements");
+    sp = scales->data_ptr();
+  }
+  if (M == 0) return;
+  if ((N % 128) != 0 || (K % 128) != 0 || N <= 0 || K <= 0) raise(FG_ERR_SHAPE, op != FG_OP_F16_KN);
+
+  const c10::cuda::CUDAGuard guard(x.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
+  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  int st;
+  {
+    pybind11::gil_scoped_release nogil;
+    fg_stream_t s = reinterpret_cast<fg_stream_t>(stream);
+    if (op == FG_OP_F16_KN)
+      st = fg_gemm_f16_kn(x.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, ws.buf.data_ptr(), ws.bytes, s);
+    else if (op == FG_OP_F16_NK)
+      st = fg_gemm_f16_nk(x.data_ptr(), W.data_ptr(), C.data_ptr(), M, N, K, ws.buf.data_ptr(), ws.bytes, s);
+    else
+      st = fg_gemm_w8a16_nk(x.data_ptr(), static_cast<const int8_t*>(W.data_ptr()), sp, C.data_ptr(), M, N, K,
+                            ws.buf.data_ptr(), ws.bytes, s);
+  }
+  if (st != FG_OK) raise(st, op != FG_OP_F16_KN);
+}
+
+// ---- the three calling conventions of the reference ---------------------------------------
+// (A[M,K], B[K,N], C)                     edgemm*, edgemv*, flat_gemm_*
+void op_kn(at::Tensor A, at::Tensor B, at::Tensor C) { linear(FG_OP_F16_KN, A, B, C, c10::nullopt); }
+// the reference's bz argument chose the split-K factor by hand; here it is accepted and ignored
+void op_kn_bz(at::Tensor A, at::Tensor B, at::Tensor C, int /*bz*/) { linear(FG_OP_F16_KN, A, B, C, c10::nullopt); }
+// (A[M,K], W[N,K], C)                     edgemm_*_bt, *_tr_amd, gemm_*_bt
+void op_nk(at::Tensor A, at::Tensor W, at::Tensor C) { linear(FG_OP_F16_NK, A, W, C, c10::nullopt); }
+void op_nk_bz(at::Tensor A, at::Tensor W, at::Tensor C, int /*bz*/) { linear(FG_OP_F16_NK, A, W, C, c10::nullopt); }
+// (W[N,K], x[M,K], C)  weight first        fastgemv*, fastgemm
+void op_wfirst(at::Tensor W, at::Tensor x, at::Tensor C) { linear(FG_OP_F16_NK, x, W, C, c10::nullopt); }
+void op_wfirst_int8(at::Tensor W8, at::Tensor x, at::Tensor C, c10::optional<at::Tensor> scales) {
+  linear(FG_OP_W8A16_NK, x, W8, C, scales);
+}
+
+// cuBLAS comparators of the reference (backend/cuda/hk/hgemm.cu:29-74, hgemm_tr.cu:30-75):
+// library calls, kept only so that scripts which import them keep working.
+void hgemm(at::Tensor A, at::Tensor B, at::Tensor C) {
+  auto out = C.view({A.size(0), B.size(1)});
+  at::matmul_out(out, A, B);
+}
+void hgemm_tr(at::Tensor A, at::Tensor W, at::Tensor C) {
+  auto out = C.view({A.size(0), W.size(0)});
+  at::matmul_out(out, A, W.t());
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "fastgate_b200: B200 (sm_100a) small-batch matmul operators with the SPEEDGATE surface";
+  namespace py = pybind11;
+  // KxN weight: backend/cuda/hk/edgemm.h:4-14
+  for (const char* n : {"edgemm", "edgemm_m8n256k64", "edgemm_m8n128k64", "edgemm_m8n128k128",
+                        "edgemv_m1n128k64x4", "edgemm_m8n128k64x4", "edgemv_m1n256k64x4",
+                        "edgemm_m8n128k64x4_amd", "edgemm_m8n256k32x8"})
+    m.def(n, &op_kn, py::arg("A"), py::arg("B"), py::arg("C"));
+  // backend/cuda/hk/flatgemm.h:4-10
+  for (const char* n : {"flat_gemm_m8n256k32x8_bz1", "flat_gemm_m8n256k32x16"})
+    m.def(n, &op_kn, py::arg("A"), py::arg("B"), py::arg("C"));
+  for (const char* n : {"flat_gemm_m8n128k64x4_bz1", "flat_gemm_m8n256k64x8", "flat_gemm_m8n512k32x16",
+                        "flat_gemm_m8n64k128x8", "flat_gemm_m8n32k256x8"})
+    m.def(n, &op_kn_bz, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("bz") = 1);
+  // NxK weight, activation first: backend/cuda/hk/edgemm.h:10,14 and edgemm_tr.h:7-11
+  for (const char* n : {"edgemm_m8n128k64x4_bt", "edgemm_m8n128k64x4_tr_amd", "gemm_m8n128k64x4_bt",
+                        "gemm_m8n32k128x8_bt", "gemm_m8n32k256x8_bt"})
+    m.def(n, &op_nk, py::arg("A"), py::arg("B"), py::arg("C"));
+  for (const char* n : {"gemm_m8n32k256x8_bt_bz2", "gemm_m8n64k128x8_bt_exp"})
+    m.def(n, &op_nk_bz, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("bz") = 1);
+  // NxK weight, weight first: backend/cuda/hk/fastgemv.h:4-7, backend/cuda/czn/fastgemm.h:4
+  for (const char* n : {"fastgemv", "fastgemv_tuned", "fastgemv_extend", "fastgemm"})
+    m.def(n, &op_wfirst, py::arg("A"), py::arg("B"), py::arg("C"));
+  m.def("fastgemv_int8", &op_wfirst_int8, py::arg("A"), py::arg("B"), py::arg("C"),
+        py::arg("scales") = py::none(),
+        "int8 weight W8[N,K], fp16 x[M,K]; scales[N] (fp16) optional: None = scale 1, zero-point 0 "
+        "as the reference launches it (backend/cuda/hk/fastgemv.cu:50-59)");
+  m.def("hgemm", &hgemm);
+  m.def("hgemm_tr", &hgemm_tr);
+  m.def("launch_count", []() { return fg_launch_count(); });
+  m.def("version", []() { return std::string(fg_version()); });
+}

@@ -1,0 +1,145 @@
+/*
+ * fastgate_b200 — C ABI of the B200 (sm_100a) small-batch matmul library.
+ *
+ * Everything a non-PyTorch caller needs is here: plain pointers and sizes, an
+ * explicit cudaStream_t, an explicit caller-owned workspace, int status codes.
+ * No entry point throws, exits, synchronises the device or allocates device
+ * memory, unless its comment says so.
+ *
+ * The library replaces the host launchers of chanzhennan/Fastgate
+ * (reference paths below are relative to that project):
+ *
+ *   backend/cuda/hk/edgemm.cu:102-156    edgemm_m8n128k64x4      C[M,N] = A[M,K] . B[K,N]
+ *   backend/cuda/hk/edgemm.cu:274-324    edgemm_m8n128k64x4_bt   C[M,N] = A[M,K] . W[N,K]^T
+ *   backend/cuda/hk/fastgemv.cu:12-33    fastgemv                y[N]   = W[N,K] . x[K]
+ *   backend/cuda/hk/fastgemv.cu:35-61    fastgemv_int8           y[N]   = s * W8[N,K] . x[K]
+ *   backend/cuda/hk/fastgemv.cu:86-111   fastgemv_extend         C[M,N] = x[M,K] . W[N,K]^T
+ *   backend/cuda/czn/fastgemm.cu:13-55   fastgemm                same, M in {1,2}
+ *   backend/cuda/hk/flatgemm.cu:13-169   flat_gemm_*             KxN weights
+ *   backend/cuda/hk/edgemm_tr.cu:19-139  gemm_*_bt               NxK weights
+ *
+ * All matrices are dense row-major.  fp16 is IEEE binary16 ("half").
+ * Contract shared with the reference (hk/edgemm.cu:107-109): K % 128 == 0 and
+ * N % 128 == 0, otherwise FG_ERR_SHAPE.  M may be any positive number; M > 16
+ * is processed in 16-row passes (the weight is streamed once per pass).
+ * Results overwrite C (C = A.B); accumulation is fp32, one rounding to fp16.
+ */
+#ifndef FASTGATE_B200_H_
+#define FASTGATE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling in the CUDA headers. */
+typedef struct CUstream_st* fg_stream_t;
+
+/* ---- status codes -------------------------------------------------------- */
+enum {
+  FG_OK = 0,
+  FG_ERR_SHAPE = 1,     /* K or N not a multiple of 128, or a size <= 0        */
+  FG_ERR_ALIGN = 2,     /* a pointer is not 16-byte aligned                    */
+  FG_ERR_NULL = 3,      /* a required pointer is NULL                          */
+  FG_ERR_WORKSPACE = 4, /* workspace missing, misaligned or too small          */
+  FG_ERR_CUDA = 5,      /* a CUDA runtime/driver call failed (see fg_last_cuda_error) */
+  FG_ERR_TIMEOUT = 6,   /* a bounded device-side wait gave up (read back with fg_workspace_status) */
+  FG_ERR_PLAN = 7,      /* a caller-supplied plan is not launchable            */
+  FG_ERR_NO_DEVICE = 8  /* no sm_100 device is current                         */
+};
+
+/* ---- operand layouts ------------------------------------------------------ */
+enum {
+  FG_OP_F16_KN = 0,  /* weight B[K,N] fp16  (edgemm_m8n128k64x4, flat_gemm_*)     */
+  FG_OP_F16_NK = 1,  /* weight W[N,K] fp16  (edgemm_*_bt, gemm_*_bt, fastgemv*)   */
+  FG_OP_W8A16_NK = 2 /* weight W8[N,K] int8 + optional fp16 scale per row of W8   */
+};
+
+/*
+ * Launch plan: the replacement for the reference's split-K choice
+ * (hk/edgemm.cu:287-305; script/heuristics.py is empty there).  The weight is cut
+ * into 128-column output tiles times k_blocks stages; that list of units is dealt
+ * out in equal contiguous ranges to `grid` persistent CTAs ("stream-K"), so every
+ * SM streams the same number of bytes whatever N/128 is.
+ */
+typedef struct fg_plan_t {
+  int op;            /* FG_OP_*                                               */
+  int m_tile;        /* 8 or 16: token rows held per accumulator tile          */
+  int k_per_stage;   /* K elements one pipeline stage covers                   */
+  int stages;        /* depth of the shared-memory ring                        */
+  int consumer_warps;/* warps doing the math; one more warp issues the copies  */
+  int grid;          /* persistent CTAs                                        */
+  int tiles;         /* N / 128                                                */
+  int k_blocks;      /* ceil(K / k_per_stage): stages per output tile          */
+  int smem_bytes;    /* dynamic shared memory per CTA                          */
+  int passes;        /* ceil(M / 16) launches                                  */
+  int math;          /* 0 = mma.sync tensor-core tiles, 1 = CUDA-core FMA (reserved) */
+} fg_plan_t;
+
+/* Pure host function (callable without a GPU): fills *out for a problem on a device
+ * with sm_count SMs and smem_optin_bytes of opt-in shared memory per CTA (pass 0/0
+ * for the B200 values 148 / 232448). */
+int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin_bytes, fg_plan_t* out);
+/* Checks a plan (e.g. one edited by a tuner) against the limits the kernel relies on. */
+int fg_plan_validate(const fg_plan_t* plan, int N, int K, int smem_optin_bytes);
+
+/* ---- workspace -------------------------------------------------------------
+ * Split-K partial tiles and per-tile arrival counters live in caller-owned device
+ * memory, 256-byte aligned.  fg_workspace_bytes() is an upper bound for any M and
+ * K at the given N.  The workspace must be cleared once with fg_workspace_init()
+ * before first use; after that every call leaves the counters at zero again, so no
+ * memset is launched per call.  One workspace serves one stream at a time: calls
+ * that may overlap on the GPU need separate workspaces. */
+size_t fg_workspace_bytes(int N);
+int fg_workspace_init(void* ws, size_t ws_bytes, fg_stream_t stream);
+/* Synchronises `stream`, copies the device status word to *status_out (FG_OK or
+ * FG_ERR_TIMEOUT) and clears it. */
+int fg_workspace_status(void* ws, int* status_out, fg_stream_t stream);
+
+/* ---- compute entry points (device pointers) --------------------------------
+ * replaces edgemm_m8n128k64x4 (hk/edgemm.cu:102-156) and the flat_gemm_* family
+ * (hk/flatgemm.cu:13-169): A[M,K], B[K,N], C[M,N], all fp16. */
+int fg_gemm_f16_kn(const void* A, const void* B, void* C, int M, int N, int K,
+                   void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* replaces edgemm_m8n128k64x4_bt (hk/edgemm.cu:274-324), gemm_*_bt
+ * (hk/edgemm_tr.cu:19-139), fastgemv / fastgemv_extend (hk/fastgemv.cu:12-33,86-111)
+ * and fastgemm (czn/fastgemm.cu:13-55): x[M,K], W[N,K], C[M,N], all fp16. */
+int fg_gemm_f16_nk(const void* x, const void* W, void* C, int M, int N, int K,
+                   void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* replaces fastgemv_int8 (hk/fastgemv.cu:35-61): x[M,K] fp16, W8[N,K] int8,
+ * scales[N] fp16 or NULL (NULL = the reference's effective scale 1, zero-point 0),
+ * C[M,N] fp16 = (x . W8^T) * scales[n]. */
+int fg_gemm_w8a16_nk(const void* x, const int8_t* W8, const void* scales, void* C,
+                     int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* Same three operations with an explicit plan (from fg_plan, possibly edited):
+ * used by the tuner and the tests that walk every plan the heuristic can emit. */
+int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const void* scales,
+                    void* C, int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* ---- end-to-end convenience (HOST pointers) ---------------------------------
+ * x_host and C_host are host buffers (pinned for full speed); W_dev, scales_dev,
+ * x_stage_dev (M*K fp16) and C_stage_dev (M*N fp16) are device buffers the caller
+ * owns.  Copies x in, runs the op, copies C out and synchronises `stream`.
+ * The weight stays resident on the device, as at the reference's call sites. */
+int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev,
+                   void* C_host, void* x_stage_dev, void* C_stage_dev, int M, int N, int K,
+                   void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* ---- diagnostics -------------------------------------------------------------- */
+const char* fg_status_str(int status);
+/* cudaError_t / CUresult of the last failing call on this host thread (0 if none). */
+int fg_last_cuda_error(void);
+/* Number of kernel launches this library has issued from this process. */
+unsigned long long fg_launch_count(void);
+/* "fastgate_b200 <version> sm_100a" */
+const char* fg_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FASTGATE_B200_H_ */
