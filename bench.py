@@ -1,0 +1,427 @@
+#!/usr/bin/env python
+"""Benchmark of the small-batch matmul hot path (one JSON line on stdout, rank 0).
+
+Workload "bt_sweep" (default): one step = five calls of edgemm_m8n128k64x4_bt,
+M in {1,2,4,8,16}, K = N = 8192 per GPU, fp16, weight stored NxK; each call streams a
+different one of four weight copies (537 MB, larger than the 126 MB L2).  With N GPUs every
+rank holds its own 8192-row shard of an (8192*N) x 8192 weight ("weak" scaling): the ranks
+compute their output slices independently and the slices are assembled with one NCCL
+all-gather per call.  `value` is the whole job's effective HBM bandwidth (algorithmic bytes
+of all ranks / time, gather included at N > 1); `no_gather` reports the same without it.
+
+  value     inputs resident in HBM, step replayed from a CUDA graph (N = 1) or launched on
+            a stream (N > 1), timed with CUDA events on the launching stream
+  e2e       the same step through the public operator (fastgate_b200.edgemm_m8n128k64x4_bt)
+            with the activations copied from pinned host memory and the result read back
+            every call; the weight stays resident, as at the reference's call sites
+  roofline  algorithmic bytes per launch / average launch duration, against the measured
+            copy bandwidth of this pool's B200s
+  cpu_baseline  the CPU oracle (a port of the reference's arithmetic, OpenMP) on this box's
+            host cores, for one step
+
+`--impl reference` times the reference's own kernels, rebuilt unmodified for sm_100a
+(oracle/_ref), on the same workload through the reference's operator; when that build is
+not available it falls back to the CPU oracle port.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+N_WEIGHT_COPIES = 4
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the M=16 case, from the ncu
+# capture summarised in profiles/ (None until one has been taken)
+NCU_TRAFFIC_BYTES_M16 = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--workload", choices=("bt_sweep",), default="bt_sweep")
+    ap.add_argument("--no-graph", action="store_true", help="launch on a stream instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--reference-arm", choices=("auto", "gpu", "cpu"), default="auto")
+    return ap.parse_args()
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples of one GPU during the timed region."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            f = [v.strip() for v in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def barrier_sync(world):
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, world: int) -> float:
+    import torch
+    import torch.distributed as dist
+
+    if world == 1:
+        return ms
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_steps(step_fn, steps: int, warmup: int, world: int, stream, graph=None) -> float:
+    """ms for exactly `steps` steps, device-timed on `stream`, max over ranks."""
+    import torch
+
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            graph.replay() if graph is not None else step_fn()
+        barrier_sync(world)
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            graph.replay() if graph is not None else step_fn()
+        e1.record(stream)
+        barrier_sync(world)
+    return max_over_ranks(e0.elapsed_time(e1), world)
+
+
+def cpu_baseline_leg(cases, sample_reps: int = 3) -> dict:
+    """The CPU oracle (port of the reference's arithmetic) on one full step, host cores."""
+    import numpy as np
+
+    from oracle import oracle
+
+    rng = np.random.default_rng(0)
+    W = (rng.standard_normal((8192, 8192)) / 90.5).astype(np.float16)
+    xs = [rng.standard_normal((c.M, c.K)).astype(np.float16) for c in cases]
+    oracle.gemm_nk(xs[0], W)  # warm-up, builds the library if needed
+    times = []
+    for _ in range(sample_reps):
+        t0 = time.perf_counter()
+        for x in xs:
+            oracle.gemm_nk(x, W)
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    bytes_step = sum(c.algorithmic_bytes for c in cases)
+    return {"value": bytes_step / sec / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"one full step (5 calls, M=1,2,4,8,16, K=N=8192), median of {sample_reps}",
+            "ms_per_step": sec * 1e3}
+
+
+def run_ours(args):
+    import torch
+
+    import fastgate_b200 as fg
+    from fastgate_b200 import shard, workloads as wl
+
+    world, rank, local = dist_setup(args)
+    dev = torch.device("cuda", local)
+    cases = wl.cfg2()
+    bytes_step_rank = sum(c.algorithmic_bytes for c in cases)
+
+    # this rank's shard of the (8192*world) x 8192 weight, four seeded copies
+    weights = []
+    for i in range(N_WEIGHT_COPIES):
+        g = torch.Generator(device="cpu").manual_seed(2000 + 97 * rank + i)
+        weights.append((torch.randn(8192, 8192, generator=g) / 8192 ** 0.5).to(torch.float16).to(dev))
+    xs_host = [wl.make_activation(c).pin_memory() for c in cases]
+    xs = [x.to(dev) for x in xs_host]
+    layers = [shard.ShardedLinear(w, 8192 * world) for w in weights]
+
+    stream = torch.cuda.Stream(device=dev)
+    state = {"i": 0}
+
+    def step_local():
+        for ci in range(len(cases)):
+            layers[(state["i"] + ci) % N_WEIGHT_COPIES].forward_local(xs[ci])
+        state["i"] += 1
+
+    def step_gather():
+        for ci in range(len(cases)):
+            layers[(state["i"] + ci) % N_WEIGHT_COPIES].forward(xs[ci])
+        state["i"] += 1
+
+    # ---- device-resident timing -------------------------------------------------------
+    graph = None
+    use_graph = (not args.no_graph) and world == 1
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step_local()
+        torch.cuda.synchronize()
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(N_WEIGHT_COPIES):  # every rotation of the copies
+                    step_local()
+
+    launches0 = fg.launch_count()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if graph is not None:
+        # one replay = N_WEIGHT_COPIES steps
+        reps = max(1, -(-args.steps // N_WEIGHT_COPIES))
+        wreps = max(1, -(-args.warmup // N_WEIGHT_COPIES))
+        ms_local = time_steps(None, reps, wreps, world, stream, graph=graph) * args.steps / (reps * N_WEIGHT_COPIES)
+        launches = reps * N_WEIGHT_COPIES * len(cases)
+    else:
+        ms_local = time_steps(step_local, args.steps, args.warmup, world, stream)
+        launches = fg.launch_count() - launches0 - args.warmup * len(cases)
+    if world > 1:
+        ms_full = time_steps(step_gather, args.steps, args.warmup, world, stream)
+    else:
+        ms_full = ms_local
+    clocks = sampler.stop() if sampler else None
+
+    # per-M device time (graph of 20 calls on rotating copies), for the breakdown
+    per_call = {}
+    if world == 1:
+        with torch.cuda.stream(stream):
+            for ci, c in enumerate(cases):
+                gg = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gg, stream=stream):
+                    for r in range(20):
+                        layers[r % N_WEIGHT_COPIES].forward_local(xs[ci])
+                gg.replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(5):
+                    gg.replay()
+                e1.record(stream)
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / 100
+                per_call[f"M{c.M}"] = {"us": round(us, 2), "GBps": round(c.algorithmic_bytes / us / 1e3, 1)}
+
+    # ---- end to end through the operator, host activations in, host result out -----------
+    e2e = None
+    if not args.no_e2e:
+        outs_host = [torch.empty(c.M, c.N, dtype=torch.float16).pin_memory() for c in cases]
+        x_stage = [torch.empty_like(x) for x in xs]
+
+        def step_e2e():
+            for ci in range(len(cases)):
+                x_stage[ci].copy_(xs_host[ci], non_blocking=True)
+                lay = layers[(state["i"] + ci) % N_WEIGHT_COPIES]
+                out = lay.forward(x_stage[ci]) if world > 1 else lay.forward_local(x_stage[ci])
+                if rank == 0 or world == 1:
+                    outs_host[ci].copy_(out[:, :cases[ci].N] if world > 1 else out, non_blocking=True)
+            state["i"] += 1
+            torch.cuda.current_stream().synchronize()  # the caller has its result
+
+        ms_e2e = time_steps(step_e2e, args.steps, args.warmup, world, stream)
+        e2e = {"value": bytes_step_rank * world / (ms_e2e / args.steps) / 1e6, "unit": "GB/s",
+               "ms_per_step": ms_e2e / args.steps,
+               "h2d_bytes_per_step": sum(x.numel() * 2 for x in xs_host),
+               "d2h_bytes_per_step": sum(o.numel() * 2 for o in outs_host)}
+
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak()
+    ms_step = ms_full / args.steps
+    ms_step_local = ms_local / args.steps
+    avg_launch_s = ms_step_local / 1e3 / len(cases)
+    avg_bytes = bytes_step_rank / len(cases)
+    achieved = avg_bytes / avg_launch_s / 1e9
+    line = {
+        "metric": "effective HBM GB/s of M<=16 fp16 GEMM-GEMV (edgemm_m8n128k64x4_bt, K=N=8192)",
+        "value": bytes_step_rank * world / ms_step / 1e6, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": "bt_sweep: edgemm_m8n128k64x4_bt, M in {1,2,4,8,16}, K=N=8192 per GPU, weight NxK fp16",
+                   "calls_per_step": len(cases), "l2": f"{N_WEIGHT_COPIES} rotating weight copies (537 MB) > 126 MB L2",
+                   "launch": "cuda graph replay" if graph is not None else "stream launches",
+                   "sharding": f"N-sharded, {world} x 8192 columns, NCCL all-gather per call" if world > 1 else "single GPU"},
+        "us_per_call": ms_step * 1e3 / len(cases),
+        "per_call": per_call,
+        "no_gather": {"value": bytes_step_rank * world / ms_step_local / 1e6, "unit": "GB/s", "ms_per_step": ms_step_local},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
+                     "traffic": NCU_TRAFFIC_BYTES_M16, "kernel": "fg::fg_streamk_kernel<1,8|16>",
+                     "algorithmic_bytes_per_launch": avg_bytes},
+        "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_baseline_leg(cases)
+    return line
+
+
+def run_reference(args):
+    """The reference's own implementation of the path: its kernels rebuilt for sm_100a when
+    available (and a GPU is present), else the CPU oracle port on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from fastgate_b200 import workloads as wl
+
+    cases = wl.cfg2()
+    bytes_step = sum(c.algorithmic_bytes for c in cases)
+    cpu = cpu_baseline_leg(cases)
+    want_gpu = args.reference_arm in ("auto", "gpu")
+    ref = None
+    if want_gpu:
+        try:
+            import torch
+
+            from oracle import ref_gpu
+            if torch.cuda.is_available():
+                ref = ref_gpu.load()
+        except Exception as e:  # unloadable build: fall back to the port
+            ref = None
+            sys.stderr.write(f"reference kernels unavailable: {e}\n")
+    base = {
+        "impl": "reference",
+        "metric": "effective HBM GB/s of M<=16 fp16 GEMM-GEMV (edgemm_m8n128k64x4_bt, K=N=8192)",
+        "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+        "config": {"workload": "bt_sweep: edgemm_m8n128k64x4_bt, M in {1,2,4,8,16}, K=N=8192 per GPU, weight NxK fp16",
+                   "calls_per_step": len(cases)},
+        "cpu_baseline": cpu,
+    }
+    if ref is None:
+        sec = cpu["ms_per_step"] / 1e3
+        base.update({"value": bytes_step / sec / 1e9, "ms_per_step": sec * 1e3, "dtype": "f32 accumulate (CPU port)",
+                     "reference_kind": "cpu oracle port (reference kernels not built or no GPU)",
+                     "e2e": {"value": bytes_step / sec / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        return base
+
+    import torch
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    weights = []
+    for i in range(N_WEIGHT_COPIES):
+        g = torch.Generator(device="cpu").manual_seed(2000 + i)
+        weights.append((torch.randn(8192, 8192, generator=g) / 8192 ** 0.5).to(torch.float16).to(dev))
+    xs_host = [wl.make_activation(c).pin_memory() for c in cases]
+    xs = [x.to(dev) for x in xs_host]
+    outs = [torch.zeros(c.M, c.N, dtype=torch.float16, device=dev) for c in cases]
+    outs_host = [torch.empty(c.M, c.N, dtype=torch.float16).pin_memory() for c in cases]
+    x_stage = [torch.empty_like(x) for x in xs]
+    state = {"i": 0}
+    # the reference launches on the legacy default stream (hk/edgemm.cu:319), so time there
+    stream = torch.cuda.default_stream(dev)
+
+    def step():
+        for ci in range(len(cases)):
+            ref.edgemm_m8n128k64x4_bt(xs[ci], weights[(state["i"] + ci) % N_WEIGHT_COPIES], outs[ci])
+        state["i"] += 1
+
+    def step_e2e():
+        for ci in range(len(cases)):
+            x_stage[ci].copy_(xs_host[ci], non_blocking=True)
+            ref.edgemm_m8n128k64x4_bt(x_stage[ci], weights[(state["i"] + ci) % N_WEIGHT_COPIES], outs[ci])
+            outs_host[ci].copy_(outs[ci], non_blocking=True)
+        state["i"] += 1
+        stream.synchronize()
+
+    sampler = ClockSampler(0)
+    ms = time_steps(step, args.steps, args.warmup, 1, stream)
+    clocks = sampler.stop()
+    ms_e2e = time_steps(step_e2e, args.steps, args.warmup, 1, stream)
+    base.update({
+        "value": bytes_step / (ms / args.steps) / 1e6, "ms_per_step": ms / args.steps,
+        "dtype": "f16 (fp16 accumulate)", "clocks": clocks,
+        "reference_kind": "reference kernels (hk/edgemm.cu:274-324) rebuilt unmodified for sm_100a, same B200",
+        "e2e": {"value": bytes_step / (ms_e2e / args.steps) / 1e6, "unit": "GB/s", "ms_per_step": ms_e2e / args.steps,
+                "h2d_bytes_per_step": sum(x.numel() * 2 for x in xs_host),
+                "d2h_bytes_per_step": sum(o.numel() * 2 for o in outs_host)},
+    })
+    return base
+
+
+def main():
+    args = parse_args()
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    try:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+    except Exception:
+        pass
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

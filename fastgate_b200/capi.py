@@ -20,7 +20,7 @@ FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK = 0, 1, 2
 EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
     "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_planned", "fg_linear_host",
-    "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
+    "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
 
@@ -29,7 +29,7 @@ class Plan(ctypes.Structure):
 
     _fields_ = [(n, ctypes.c_int) for n in (
         "op", "m_tile", "k_per_stage", "stages", "consumer_warps", "grid", "tiles", "k_blocks",
-        "smem_bytes", "passes", "math")]
+        "smem_bytes", "passes", "math", "pdl")]
 
     def as_dict(self) -> dict:
         return {n: getattr(self, n) for n, _ in self._fields_}
@@ -53,6 +53,8 @@ def _load() -> ctypes.CDLL:
     L.fg_gemm_w8a16_nk.argtypes = [vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_planned.argtypes = [ctypes.POINTER(Plan), vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_trace_enable.argtypes = [i]
+    L.fg_trace_read.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong), i, vp]
     L.fg_status_str.argtypes = [i]
     L.fg_status_str.restype = ctypes.c_char_p
     L.fg_last_cuda_error.restype = i

@@ -27,6 +27,9 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
 namespace {
 
 thread_local int g_last_cuda = 0;
+std::atomic<int> g_trace{0};
+// The tracer borrows the partial-tile slots of CTAs 200.. (unused while grid <= 200).
+constexpr int kTraceFirstCta = 200;
 std::atomic<unsigned long long> g_launches{0};
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -161,6 +164,10 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.partials = reinterpret_cast<float*>(wsb + FG_WS_HEADER_BYTES);
   p.tickets = reinterpret_cast<unsigned int*>(wsb + FG_WS_TICKETS_OFFSET);
   p.status = reinterpret_cast<int*>(wsb);
+  p.trace = nullptr;
+  if (g_trace.load(std::memory_order_relaxed) && pl.grid <= kTraceFirstCta)
+    p.trace = reinterpret_cast<unsigned long long*>(wsb + FG_WS_HEADER_BYTES +
+                                                    static_cast<size_t>(kTraceFirstCta) * 2 * FG_WS_PARTIAL_TILE_BYTES);
   p.N = N;
   p.K = K;
   p.tiles = pl.tiles;
@@ -168,6 +175,7 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.chunks_per_stage = chunks;
   p.stages = pl.stages;
   p.consumer_warps = pl.consumer_warps;
+  p.pdl = pl.pdl ? 1 : 0;
 
   for (int m0 = 0; m0 < M; m0 += 16) {
     const int mp = (M - m0) < 16 ? (M - m0) : 16;
@@ -178,8 +186,18 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     if (st != FG_OK) return st;
     p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * N;
     p.M = mp;
-    kern<<<pl.grid, (pl.consumer_warps + 1) * 32, pl.smem_bytes, stream>>>(tmW, tmX, p);
-    const cudaError_t e = cudaGetLastError();
+    // consumer warps + one copy-issuing warp + one warp that finishes split tiles
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.grid);
+    cfg.blockDim = dim3((pl.consumer_warps + 2) * 32);
+    cfg.dynamicSmemBytes = pl.smem_bytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pl.pdl ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
     if (e != cudaSuccess) {
       g_last_cuda = static_cast<int>(e);
       return FG_ERR_CUDA;
@@ -283,6 +301,28 @@ int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* sc
   if (st != FG_OK) return st;
   e = cudaMemcpyAsync(C_host, C_stage_dev, static_cast<size_t>(M) * N * 2, cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  return FG_OK;
+}
+
+int fg_trace_enable(int on) {
+  g_trace.store(on ? 1 : 0, std::memory_order_relaxed);
+  return FG_OK;
+}
+
+int fg_trace_read(void* ws, unsigned long long* out, int ctas, fg_stream_t stream) {
+  if (ws == nullptr || out == nullptr) return FG_ERR_NULL;
+  if (ctas < 1 || ctas > kTraceFirstCta) return FG_ERR_PLAN;  // 64 B per CTA, far below the borrowed slots
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  uint8_t* src = static_cast<uint8_t*>(ws) + FG_WS_HEADER_BYTES +
+                 static_cast<size_t>(kTraceFirstCta) * 2 * FG_WS_PARTIAL_TILE_BYTES;
+  const size_t bytes = static_cast<size_t>(ctas) * 8 * sizeof(unsigned long long);
+  cudaError_t e = cudaMemcpyAsync(out, src, bytes, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(src, 0, bytes, s);
   if (e != cudaSuccess) {
     g_last_cuda = static_cast<int>(e);
     return FG_ERR_CUDA;

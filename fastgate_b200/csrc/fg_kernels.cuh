@@ -17,6 +17,11 @@
 // the partials in CTA order (deterministic) and writes C.  Nobody waits on another
 // CTA, and every mbarrier wait is bounded in time.
 //
+// Ring discipline: CTA-local stage number `it` uses ring slot it % stages and is consumed
+// by warp it % consumer_warps.  stages % consumer_warps == 0 (enforced by the planner), so
+// a slot always meets the same warp and that warp observes every phase of the slot's
+// barriers: an mbarrier parity wait is only meaningful to a waiter that misses no phase.
+//
 // Replaces eed_hgemm_m8n128k64x4_v7 / _v7_bt (backend/cuda/hk/edgemm.cuh:1669-1868,
 // 1467-1667), gemv_fp16 / gemm_fp16 / gemv_quantized_int8
 // (backend/cuda/hk/fastgemv.cuh:503-562, 244-311, 316-389) and gemv_fp16_bs2
@@ -63,12 +68,14 @@ struct KParams {
   float* partials;           // [grid][2][MT * 128]
   unsigned int* tickets;     // [tiles], zero between launches
   int* status;               // device status word
+  unsigned long long* trace; // nullptr, or 8 timestamps (ns) per CTA for the built-in tracer
   int M, N, K;
   int tiles;                 // N / 128
   int k_blocks;              // stages per tile
   int chunks_per_stage;
   int stages;
   int consumer_warps;
+  int pdl;                   // 1: launched with programmatic stream serialization
 };
 
 __host__ __device__ constexpr int chunk_bytes(int op, int mt) {
@@ -96,90 +103,139 @@ __device__ __forceinline__ void load_b_frags_f16(uint32_t xbase, int kk2, int q,
   }
 }
 
+// Weight fragments of all eight 16-row groups for one k16 step (fp16 ops).
+template <int OP>
+__device__ __forceinline__ void load_a_frags_f16(uint32_t wbase, int kk, int q, int r,
+                                                 uint32_t (&a)[8][4]) {
+#pragma unroll
+  for (int rg = 0; rg < 8; ++rg) {
+    if constexpr (OP == kOpF16NK) {
+      // weight chunk [128 n][64 k]: rows are output columns
+      const uint32_t addr =
+          wbase + (rg * 16 + (q & 1) * 8 + r) * 128 + ((((kk * 2) + (q >> 1)) ^ r) << 4);
+      ldsm_x4(addr, a[rg][0], a[rg][1], a[rg][2], a[rg][3]);
+    } else {
+      // weight chunk = two boxes [64 k][64 n]: rows are k, transpose on load
+      const int krow = kk * 16 + (q >> 1) * 8 + r;
+      const uint32_t addr =
+          wbase + (rg >> 2) * 8192 + krow * 128 + (((((rg & 3) * 2) + (q & 1)) ^ r) << 4);
+      ldsm_x4_trans(addr, a[rg][0], a[rg][1], a[rg][2], a[rg][3]);
+    }
+  }
+}
+
 template <int OP, int MT>
 __device__ __forceinline__ void consume_chunk(uint32_t wbase, uint32_t xbase, int lane,
                                               float (&acc)[8][MT / 8][4]) {
   const int q = lane >> 3, r = lane & 7;
   if constexpr (OP == kOpF16NK || OP == kOpF16KN) {
+    // Software pipeline over the four k16 steps: the fragments of step kk+1 are in flight
+    // while the tensor-core ops of step kk issue.
+    uint32_t a[2][8][4];
+    uint32_t b[2][MT / 8][2];
+    load_a_frags_f16<OP>(wbase, 0, q, r, a[0]);
 #pragma unroll
-    for (int kk2 = 0; kk2 < 2; ++kk2) {
-      uint32_t b[2][MT / 8][2];
-      load_b_frags_f16<MT>(xbase, kk2, q, r, b);
+    for (int kk = 0; kk < 4; ++kk) {
+      if ((kk & 1) == 0) load_b_frags_f16<MT>(xbase, kk >> 1, q, r, b);
+      if (kk < 3) load_a_frags_f16<OP>(wbase, kk + 1, q, r, a[(kk + 1) & 1]);
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int kk = kk2 * 2 + e;
+      for (int rg = 0; rg < 8; ++rg)
 #pragma unroll
-        for (int rg = 0; rg < 8; ++rg) {
-          uint32_t a0, a1, a2, a3;
-          if constexpr (OP == kOpF16NK) {
-            // weight chunk [128 n][64 k]: rows are output columns
-            const uint32_t addr = wbase + (rg * 16 + (q & 1) * 8 + r) * 128 +
-                                  ((((kk * 2) + (q >> 1)) ^ r) << 4);
-            ldsm_x4(addr, a0, a1, a2, a3);
-          } else {
-            // weight chunk = two boxes [64 k][64 n]: rows are k, transpose on load
-            const int krow = kk * 16 + (q >> 1) * 8 + r;
-            const uint32_t addr = wbase + (rg >> 2) * 8192 + krow * 128 +
-                                  (((((rg & 3) * 2) + (q & 1)) ^ r) << 4);
-            ldsm_x4_trans(addr, a0, a1, a2, a3);
-          }
-#pragma unroll
-          for (int j = 0; j < MT / 8; ++j) mma_16816(acc[rg][j], a0, a1, a2, a3, b[e][j][0], b[e][j][1]);
-        }
-      }
+        for (int j = 0; j < MT / 8; ++j)
+          mma_16816(acc[rg][j], a[kk & 1][rg][0], a[kk & 1][rg][1], a[kk & 1][rg][2], a[kk & 1][rg][3],
+                    b[kk & 1][j][0], b[kk & 1][j][1]);
     }
   } else {
     // int8 weight chunk [128 n][128 k].  Within a k16 step the thread with t = lane % 4
     // owns bytes 4t..4t+3 of its rows; they are fed as MMA columns (2t, 2t+1, 2t+8, 2t+9),
     // and the activation fragment is read with the same permutation (8 contiguous bytes).
+    //
+    // The chunk is summed into a fresh accumulator that is then added to the running one
+    // with an ordinary fp32 add: the running sums of unscaled int8 products reach several
+    // thousand, where the tensor core's own accumulate step is too coarse for outputs that
+    // end near zero.
     const int g = lane >> 2, t = lane & 3;
+    uint32_t b[8][MT / 8][2];
 #pragma unroll
-    for (int cp = 0; cp < 4; ++cp) {
-      uint32_t b[2][MT / 8][2];
+    for (int s = 0; s < 8; ++s)
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int s = cp * 2 + e;
+      for (int j = 0; j < MT / 8; ++j) {
+        const int m = j * 8 + g;
+        const uint32_t addr = xbase + (s >> 2) * (MT * 128) + m * 128 +
+                              (((((s & 3) * 2) + (t >> 1)) ^ (m & 7)) << 4) + (t & 1) * 8;
+        lds_v2(addr, b[s][j][0], b[s][j][1]);
+      }
 #pragma unroll
-        for (int j = 0; j < MT / 8; ++j) {
-          const int m = j * 8 + g;
-          const uint32_t addr = xbase + (s >> 2) * (MT * 128) + m * 128 +
-                                (((((s & 3) * 2) + (t >> 1)) ^ (m & 7)) << 4) + (t & 1) * 8;
-          lds_v2(addr, b[e][j][0], b[e][j][1]);
+    for (int rp = 0; rp < 4; ++rp) {  // two 16-row groups at a time: four independent chains
+      uint32_t w[2][4][4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {
+          const int rg = rp * 2 + h;
+          const uint32_t addr =
+              wbase + (rg * 16 + (q & 1) * 8 + r) * 128 + ((((cp * 2) + (q >> 1)) ^ r) << 4);
+          ldsm_x4(addr, w[h][cp][0], w[h][cp][1], w[h][cp][2], w[h][cp][3]);
         }
-      }
+      float tmp[2][MT / 8][4];
 #pragma unroll
-      for (int rg = 0; rg < 8; ++rg) {
-        uint32_t w0, w1, w2, w3;
-        const uint32_t addr =
-            wbase + (rg * 16 + (q & 1) * 8 + r) * 128 + ((((cp * 2) + (q >> 1)) ^ r) << 4);
-        ldsm_x4(addr, w0, w1, w2, w3);
-        uint32_t lo0, hi0, lo1, hi1;
-        dequant_s8x4(w0, lo0, hi0);
-        dequant_s8x4(w1, lo1, hi1);
+      for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int j = 0; j < MT / 8; ++j) mma_16816(acc[rg][j], lo0, lo1, hi0, hi1, b[0][j][0], b[0][j][1]);
-        dequant_s8x4(w2, lo0, hi0);
-        dequant_s8x4(w3, lo1, hi1);
+        for (int j = 0; j < MT / 8; ++j)
 #pragma unroll
-        for (int j = 0; j < MT / 8; ++j) mma_16816(acc[rg][j], lo0, lo1, hi0, hi1, b[1][j][0], b[1][j][1]);
-      }
+          for (int i = 0; i < 4; ++i) tmp[h][j][i] = 0.f;
+#pragma unroll
+      for (int cp = 0; cp < 4; ++cp)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t lo0, hi0, lo1, hi1;
+          dequant_s8x4(w[h][cp][0], lo0, hi0);
+          dequant_s8x4(w[h][cp][1], lo1, hi1);
+#pragma unroll
+          for (int j = 0; j < MT / 8; ++j)
+            mma_16816(tmp[h][j], lo0, lo1, hi0, hi1, b[cp * 2][j][0], b[cp * 2][j][1]);
+          dequant_s8x4(w[h][cp][2], lo0, hi0);
+          dequant_s8x4(w[h][cp][3], lo1, hi1);
+#pragma unroll
+          for (int j = 0; j < MT / 8; ++j)
+            mma_16816(tmp[h][j], lo0, lo1, hi0, hi1, b[cp * 2 + 1][j][0], b[cp * 2 + 1][j][1]);
+        }
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < MT / 8; ++j)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[rp * 2 + h][j][i] += tmp[h][j][i];
     }
   }
 }
 
-// First unit of CTA c when `total` units are dealt to `grid` CTAs.
-__device__ __forceinline__ long long range_begin(long long c, long long total, long long grid) {
+// First unit of CTA c when `total` units are dealt to `grid` CTAs.  The host guarantees
+// total * grid < 2^31, so 32-bit arithmetic is exact.
+__device__ __forceinline__ uint32_t range_begin(uint32_t c, uint32_t total, uint32_t grid) {
   return (c * total) / grid;
 }
-__device__ __forceinline__ int cta_of_unit(long long u, long long total, long long grid) {
-  long long c = (u * grid) / total;
+__device__ __forceinline__ uint32_t cta_of_unit(uint32_t u, uint32_t total, uint32_t grid) {
+  uint32_t c = (u * grid) / total;
   while (c + 1 < grid && range_begin(c + 1, total, grid) <= u) ++c;
   while (c > 0 && range_begin(c, total, grid) > u) --c;
-  return static_cast<int>(c);
+  return c;
 }
 
+// Scale (int8 op), round and store two adjacent outputs of row m.
+template <int OP>
+__device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float2 v) {
+  if (OP == kOpW8A16NK && p.scales != nullptr) {
+    const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(p.scales + n));
+    v.x *= sc.x;
+    v.y *= sc.y;
+  }
+  *reinterpret_cast<__half2*>(p.C + static_cast<size_t>(m) * p.N + n) = __floats2half2_rn(v.x, v.y);
+}
+
+// Warp roles: [0, ncw) consume, ncw produces (TMA), ncw + 1 finishes split tiles.
 template <int OP, int MT>
-__global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
+__global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
     fg_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                       const KParams p) {
   using T = OpTraits<OP>;
@@ -195,28 +251,33 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
   const uint32_t ring_bytes = S * stage_bytes;
   float* red = reinterpret_cast<float*>(smem_gen + ring_bytes);
   const uint32_t red_bytes = ncw * MT * kRedStride * 4;
-  const uint32_t bar_base = smem_base + ring_bytes + red_bytes;  // full[S] then empty[S]
-  volatile int* flags = reinterpret_cast<volatile int*>(smem_gen + ring_bytes + red_bytes + 16 * S);
+  const uint32_t bar_base = smem_base + ring_bytes + red_bytes;  // full[S], empty[S], flush, fin
+  const uint32_t bar_flush = bar_base + 16 * S;     // consumers -> finisher: "my partial is stored"
+  const uint32_t bar_fin = bar_base + 16 * S + 8;   // finisher -> consumers: "previous partial handled"
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int nct = ncw * 32;
+  unsigned long long* trace = p.trace ? p.trace + 8 * blockIdx.x : nullptr;
+  if (trace && threadIdx.x == 0) trace[0] = globaltimer_ns();  // CTA start
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(bar_base + 8 * s, 1);        // full: one arrive (the producer's expect_tx)
       mbar_init(bar_base + 8 * (S + s), 1);  // empty: one arrive (the consuming warp's lane 0)
     }
-    flags[0] = 0;
+    mbar_init(bar_flush, nct);
+    mbar_init(bar_fin, 1);
     fence_mbar_init();
     fence_proxy_async();
   }
   __syncthreads();
 
-  const long long total = static_cast<long long>(p.tiles) * p.k_blocks;
-  const long long G = gridDim.x;
-  const long long ub = range_begin(blockIdx.x, total, G);
-  const long long ue = range_begin(blockIdx.x + 1, total, G);
-  const int KB = p.k_blocks;
+  const uint32_t KB = p.k_blocks;
+  const uint32_t total = static_cast<uint32_t>(p.tiles) * KB;
+  const uint32_t G = gridDim.x;
+  const uint32_t ub = range_begin(blockIdx.x, total, G);
+  const uint32_t ue = range_begin(blockIdx.x + 1, total, G);
   const int k_per_stage = cps * T::chunkK;
 
   if (warp == ncw) {
@@ -231,38 +292,80 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
       const int n_it = static_cast<int>(ue - ub);
       bool dead = false;
       int issued = 0;
-      for (int it = 0; it < n_it; ++it) {
+      if (trace) trace[1] = globaltimer_ns();  // first copy about to be issued
+
+      auto stage_chunks = [&](int kblock) {
+        const int k0 = kblock * k_per_stage;
+        const int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
+        return nch < cps ? nch : cps;
+      };
+      auto issue_w = [&](int s, int tl, int kblock, int nch) {
+        const uint32_t full = bar_base + 8 * s;
+        uint32_t dst = smem_base + s * stage_bytes;
+        for (int c = 0; c < nch; ++c) {
+          const int kc = kblock * k_per_stage + c * T::chunkK;
+          if constexpr (OP == kOpF16KN) {
+            tma_load_2d(dst, &tmW, full, tl * kTileN, kc, pol_w);
+            tma_load_2d(dst + 8192, &tmW, full, tl * kTileN + 64, kc, pol_w);
+          } else {
+            tma_load_2d(dst, &tmW, full, kc, tl * kTileN, pol_w);
+          }
+          dst += cbytes;
+        }
+      };
+      auto issue_x = [&](int s, int kblock, int nch) {
+        const uint32_t full = bar_base + 8 * s;
+        uint32_t dst = smem_base + s * stage_bytes + kChunkWBytes;
+        for (int c = 0; c < nch; ++c) {
+          const int kc = kblock * k_per_stage + c * T::chunkK;
+#pragma unroll
+          for (int xb = 0; xb < T::xBoxes; ++xb)
+            tma_load_2d(dst + xb * MT * 128, &tmX, full, kc + xb * 64, 0, pol_x);
+          dst += cbytes;
+        }
+      };
+
+      int it = 0;
+      if (p.pdl) {
+        // Programmatic dependent launch: this grid may start while the previous kernel of
+        // the stream is still draining.  The weight never depends on that kernel, so the
+        // first ring-full of weight tiles is requested right away; activations (which may be
+        // the previous kernel's output) only after griddepcontrol.wait.
+        griddep_launch_dependents();
+        const int pre = n_it < S ? n_it : S;
+        int t2 = tile, k2 = kb;
+        for (int i = 0; i < pre; ++i) {
+          const int nch = stage_chunks(k2);
+          mbar_arrive_expect_tx(bar_base + 8 * i, nch * cbytes);
+          issue_w(i, t2, k2, nch);
+          if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
+        }
+        griddep_wait();
+        for (int i = 0; i < pre; ++i) {
+          issue_x(i, kb, stage_chunks(kb));
+          if (++kb == static_cast<int>(KB)) { kb = 0; ++tile; }
+        }
+        it = pre;
+        issued = pre;
+      }
+      for (; it < n_it; ++it) {
         const int s = it % S;
         const uint32_t use = it / S;
         if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
           dead = true;
           break;
         }
-        const int k0 = kb * k_per_stage;
-        int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
-        nch = nch < cps ? nch : cps;
-        const uint32_t full = bar_base + 8 * s;
-        mbar_arrive_expect_tx(full, nch * cbytes);
-        uint32_t dst = smem_base + s * stage_bytes;
-        for (int c = 0; c < nch; ++c) {
-          const int kc = k0 + c * T::chunkK;
-          if constexpr (OP == kOpF16KN) {
-            tma_load_2d(dst, &tmW, full, tile * kTileN, kc, pol_w);
-            tma_load_2d(dst + 8192, &tmW, full, tile * kTileN + 64, kc, pol_w);
-          } else {
-            tma_load_2d(dst, &tmW, full, kc, tile * kTileN, pol_w);
-          }
-#pragma unroll
-          for (int xb = 0; xb < T::xBoxes; ++xb)
-            tma_load_2d(dst + kChunkWBytes + xb * MT * 128, &tmX, full, kc + xb * 64, 0, pol_x);
-          dst += cbytes;
-        }
+        const int nch = stage_chunks(kb);
+        mbar_arrive_expect_tx(bar_base + 8 * s, nch * cbytes);
+        issue_w(s, tile, kb, nch);
+        issue_x(s, kb, nch);
         ++issued;
-        if (++kb == KB) {
+        if (++kb == static_cast<int>(KB)) {
           kb = 0;
           ++tile;
         }
       }
+      if (trace) trace[2] = globaltimer_ns();  // last copy issued
       if (dead) {
         atomicExch(p.status, kStatusTimeout);
         // let copies already in flight land before the CTA's shared memory goes away
@@ -274,20 +377,106 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
     return;
   }
 
+  if (warp == ncw + 1) {
+    // ------------------------------ finisher warp ------------------------------
+    // Walks the same segment list as the consumers.  For every partial segment it waits
+    // until all consumer threads have stored their share of the partial tile, publishes it
+    // (fence + ticket) and, if this CTA was the last contributor of the tile, adds up all
+    // partials in CTA order and writes C.  The consumers meanwhile go on streaming.
+    uint32_t u = ub;
+    uint32_t ev = 0;
+    bool dead = false;
+    while (u < ue) {
+      const uint32_t tile = u / KB;
+      const uint32_t kb0 = u - tile * KB;
+      const uint32_t len = (KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u);
+      if (len != KB && !dead) {
+        bool ok = mbar_wait_bounded(bar_flush, ev & 1, kWaitBudgetNs * 4);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          dead = true;
+          if (lane == 0) atomicExch(p.status, kStatusTimeout);
+        } else {
+          const uint32_t c_first = cta_of_unit(tile * KB, total, G);
+          const uint32_t c_last = cta_of_unit(tile * KB + KB - 1, total, G);
+          const uint32_t n_contrib = c_last - c_first + 1;
+          unsigned int prev = 0;
+          if (lane == 0) {
+            __threadfence();
+            prev = atomicAdd(p.tickets + tile, 1u);
+          }
+          prev = __shfl_sync(0xffffffffu, prev, 0);
+          if (prev == n_contrib - 1) {
+            __threadfence();
+            // Lane l owns columns 4l..4l+3 of every row.  Rows go four at a time and
+            // contributors four at a time, so sixteen 16-byte loads are in flight; each
+            // element is still summed in CTA order, which keeps the result deterministic.
+            const int n0 = tile * kTileN + 4 * lane;
+            for (int m0 = 0; m0 < MT && m0 < p.M; m0 += 4) {
+              float4 sum[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (uint32_t c0 = c_first; c0 <= c_last; c0 += 4) {
+                float4 v[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t c = c0 + j;
+                  if (c <= c_last) {
+                    const uint32_t cslot = (range_begin(c, total, G) / KB == tile) ? 0u : 1u;
+                    const float4* src = reinterpret_cast<const float4*>(
+                        p.partials + (static_cast<size_t>(c) * 2 + cslot) * (MT * kTileN));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[j][i] = __ldcg(src + (m0 + i) * 32 + lane);
+                  } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) v[j][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    sum[i].x += v[j][i].x;
+                    sum[i].y += v[j][i].y;
+                    sum[i].z += v[j][i].z;
+                    sum[i].w += v[j][i].w;
+                  }
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int m = m0 + i;
+                if (m < p.M) {
+                  store_out2<OP>(p, m, n0, make_float2(sum[i].x, sum[i].y));
+                  store_out2<OP>(p, m, n0 + 2, make_float2(sum[i].z, sum[i].w));
+                }
+              }
+            }
+            if (lane == 0) p.tickets[tile] = 0;  // ready for the next launch
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_fin);
+        ++ev;
+      }
+      u += len;
+    }
+    if (trace && lane == 0) trace[5] = globaltimer_ns();  // finisher done
+    return;
+  }
+
   // -------------------------------- consumer warps --------------------------------
   const int ctid = threadIdx.x;  // consumers are warps 0..ncw-1
-  const int nct = ncw * 32;
   const int g = lane >> 2, t = lane & 3;
   bool dead = false;
-  long long u = ub;
-  int it0 = 0;  // CTA-local index of the first stage of the current segment
+  uint32_t u = ub;
+  uint32_t ev = 0;  // partial segments flushed so far
+  int it0 = 0;      // CTA-local index of the first stage of the current segment
   float acc[8][MT / 8][4];
 
   while (u < ue) {
-    const int tile = static_cast<int>(u / KB);
-    const int kb0 = static_cast<int>(u % KB);
-    const long long rest = ue - u;
-    const int len = (KB - kb0) < rest ? (KB - kb0) : static_cast<int>(rest);
+    const uint32_t tile = u / KB;
+    const int kb0 = static_cast<int>(u - tile * KB);
+    const int len = static_cast<int>((KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u));
 
 #pragma unroll
     for (int rg = 0; rg < 8; ++rg)
@@ -297,7 +486,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
         for (int i = 0; i < 4; ++i) acc[rg][j][i] = 0.f;
 
     // stages of this segment that belong to this warp: CTA-local index == warp (mod ncw)
-    int first = it0 + ((warp - it0 % ncw) + ncw) % ncw;
+    const int first = it0 + ((warp - it0 % ncw) + ncw) % ncw;
     for (int it = first; it < it0 + len && !dead; it += ncw) {
       const int s = it % S;
       const uint32_t use = it / S;
@@ -308,6 +497,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
         if (lane == 0) atomicExch(p.status, kStatusTimeout);
         break;
       }
+      if (trace && it == 0 && lane == 0) trace[3] = globaltimer_ns();  // first stage landed
       const int k0 = (kb0 + (it - it0)) * k_per_stage;
       int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
       nch = nch < cps ? nch : cps;
@@ -320,6 +510,7 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
       if (lane == 0) mbar_arrive(bar_base + 8 * (S + s));
     }
 
+    if (trace && ctid == 0) trace[4] = globaltimer_ns();  // warp 0 done with the segment's math
     // ---- cross-warp reduction of the K split (fixed order: warp 0, 1, ...) ----
     float* myred = red + warp * (MT * kRedStride);
 #pragma unroll
@@ -332,9 +523,20 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
         myred[m * kRedStride + n + 8] = acc[rg][j][2];
         myred[(m + 1) * kRedStride + n + 8] = acc[rg][j][3];
       }
+    const bool whole = (len == static_cast<int>(KB));
+    if (!whole && ev >= 1) {
+      // the finisher must have seen the previous partial before the next one is announced
+      // (both sides then observe every phase of bar_flush / bar_fin); normally long done
+      bool ok = mbar_wait_bounded(bar_fin, (ev - 1) & 1, kWaitBudgetNs * 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok && !dead) {
+        dead = true;
+        if (lane == 0) atomicExch(p.status, kStatusTimeout);
+      }
+    }
     named_bar_sync(1, nct);
+    if (trace && ctid == 0) trace[7] = globaltimer_ns();  // all warps done with the segment's math
 
-    const bool whole = (len == KB);
     const int slot = (u == ub) ? 0 : 1;
     float* mypart = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MT * kTileN);
     for (int e = ctid; e < MT * 64; e += nct) {
@@ -346,57 +548,17 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 1) * 32, 1)
         v.y += a.y;
       }
       if (whole) {
-        if (m < p.M) {
-          const int n = tile * kTileN + n2;
-          if (OP == kOpW8A16NK && p.scales != nullptr) {
-            const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(p.scales + n));
-            v.x *= sc.x;
-            v.y *= sc.y;
-          }
-          *reinterpret_cast<__half2*>(p.C + static_cast<size_t>(m) * p.N + n) = __floats2half2_rn(v.x, v.y);
-        }
+        if (m < p.M) store_out2<OP>(p, m, tile * kTileN + n2, v);
       } else {
         *reinterpret_cast<float2*>(mypart + 2 * e) = v;
       }
     }
-
     if (!whole) {
-      // ---- split tile: publish the partial, the last CTA to arrive finishes the tile ----
-      __threadfence();
-      named_bar_sync(1, nct);
-      const long long tb = static_cast<long long>(tile) * KB;
-      const int c_first = cta_of_unit(tb, total, G);
-      const int c_last = cta_of_unit(tb + KB - 1, total, G);
-      if (ctid == 0) {
-        const unsigned int prev = atomicAdd(p.tickets + tile, 1u);
-        flags[0] = (prev == static_cast<unsigned int>(c_last - c_first)) ? 1 : 0;
-      }
-      named_bar_sync(1, nct);
-      if (flags[0]) {
-        __threadfence();
-        for (int e = ctid; e < MT * 64; e += nct) {
-          const int m = e >> 6, n2 = (e & 63) * 2;
-          if (m >= p.M) continue;
-          float2 v = make_float2(0.f, 0.f);
-          for (int c = c_first; c <= c_last; ++c) {
-            const int cslot = (static_cast<int>(range_begin(c, total, G) / KB) == tile) ? 0 : 1;
-            const float2 a = __ldcg(reinterpret_cast<const float2*>(
-                p.partials + (static_cast<size_t>(c) * 2 + cslot) * (MT * kTileN) + 2 * e));
-            v.x += a.x;
-            v.y += a.y;
-          }
-          const int n = tile * kTileN + n2;
-          if (OP == kOpW8A16NK && p.scales != nullptr) {
-            const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(p.scales + n));
-            v.x *= sc.x;
-            v.y *= sc.y;
-          }
-          *reinterpret_cast<__half2*>(p.C + static_cast<size_t>(m) * p.N + n) = __floats2half2_rn(v.x, v.y);
-        }
-        if (ctid == 0) p.tickets[tile] = 0;  // ready for the next launch
-      }
+      mbar_arrive(bar_flush);  // release: this thread's share of the partial tile is stored
+      ++ev;
     }
-    named_bar_sync(1, nct);  // `red` and flags[0] are free again
+    named_bar_sync(1, nct);  // `red` is free again
+    if (trace && ctid == 0) trace[6] += 1;  // segments of this CTA
 
     u += len;
     it0 += len;

@@ -31,28 +31,35 @@ extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin
   p.tiles = N / 128;
 
   const int chunk_k = fg_chunk_k(op);
-  // Two 16 KB weight chunks per stage halve the number of barrier round trips; one chunk
-  // per stage keeps more, smaller stages in flight when a CTA has little work.
-  int chunks = 2;
-  const long long units1 = static_cast<long long>(p.tiles) * ((K + chunk_k - 1) / chunk_k);
-  if (units1 < 8LL * sm_count) chunks = 1;
-  p.consumer_warps = 4;
-
+  // One 16 KB weight chunk per stage: measured on B200, deeper rings of small stages beat
+  // fewer large ones for every shape tried (the ring is what a dependent launch prefetches
+  // while its predecessor drains).
+  const int chunks = 1;
   p.k_per_stage = chunks * chunk_k;
   p.k_blocks = (K + p.k_per_stage - 1) / p.k_per_stage;
   const long long units = static_cast<long long>(p.tiles) * p.k_blocks;
   p.grid = static_cast<int>(std::min<long long>(std::min(sm_count, FG_MAX_GRID), units));
+  if (units * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;  // beyond the kernel's 32-bit index math
 
+  // Consumer warps, from sweeps on B200: the int8 path is happiest with 3 (its dequantising
+  // inner loop keeps the issue slots busy), fp16 with 4 for an 8-row tile and 8 for 16 rows.
+  // A ring stage is always consumed by the same warp (stage s belongs to warp s % warps),
+  // which needs stages % warps == 0: a warp then sees every phase of the barriers it waits
+  // on.  The ring takes all the shared memory that is left.
+  int warps = (op == FG_OP_W8A16_NK) ? 3 : (p.m_tile == 16 ? 8 : 4);
   const int stage_bytes = chunks * fg_chunk_bytes(op, p.m_tile);
-  const int fixed = fg_fixed_smem_bytes(p.consumer_warps, p.m_tile);
-  int stages = (smem_optin_bytes - fixed) / (stage_bytes + 16);
-  stages = std::min(stages, FG_MAX_STAGES);
-  // no point in a ring deeper than the work of one CTA
-  const long long per_cta = (units + p.grid - 1) / p.grid;
-  stages = static_cast<int>(std::min<long long>(stages, std::max<long long>(per_cta, 2)));
-  if (stages < 2) return FG_ERR_PLAN;
+  int stages = 0;
+  for (; warps >= 1; --warps) {
+    const int fixed = fg_fixed_smem_bytes(warps, p.m_tile);
+    stages = (smem_optin_bytes - fixed) / (stage_bytes + 16);
+    stages = std::min(stages, FG_MAX_STAGES) / warps * warps;
+    if (stages >= 2 && stages >= warps) break;
+  }
+  if (warps < 1) return FG_ERR_PLAN;
+  p.consumer_warps = warps;
   p.stages = stages;
-  p.smem_bytes = fg_smem_bytes(op, p.m_tile, chunks, stages, p.consumer_warps);
+  p.pdl = 1;
+  p.smem_bytes = fg_smem_bytes(op, p.m_tile, chunks, p.stages, p.consumer_warps);
   *out = p;
   return FG_OK;
 }
@@ -69,10 +76,13 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (chunks < 1 || chunks > 4) return FG_ERR_PLAN;
   if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
   if (p->stages < 2 || p->stages > FG_MAX_STAGES) return FG_ERR_PLAN;
+  // each stage must always meet the same consumer warp (see fg_plan)
+  if (p->stages % p->consumer_warps) return FG_ERR_PLAN;
   if (p->tiles != N / 128) return FG_ERR_PLAN;
   if (p->k_blocks != (K + p->k_per_stage - 1) / p->k_per_stage) return FG_ERR_PLAN;
   const long long units = static_cast<long long>(p->tiles) * p->k_blocks;
   if (p->grid < 1 || p->grid > FG_MAX_GRID || p->grid > units) return FG_ERR_PLAN;
+  if (units * p->grid >= (1LL << 31)) return FG_ERR_PLAN;  // the kernel's index math is 32-bit
   if (p->smem_bytes != fg_smem_bytes(p->op, p->m_tile, chunks, p->stages, p->consumer_warps))
     return FG_ERR_PLAN;
   if (p->smem_bytes > smem_optin_bytes) return FG_ERR_PLAN;

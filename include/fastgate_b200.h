@@ -69,13 +69,16 @@ typedef struct fg_plan_t {
   int m_tile;        /* 8 or 16: token rows held per accumulator tile          */
   int k_per_stage;   /* K elements one pipeline stage covers                   */
   int stages;        /* depth of the shared-memory ring                        */
-  int consumer_warps;/* warps doing the math; one more warp issues the copies  */
+  int consumer_warps;/* warps doing the math (+1 warp issuing copies, +1 finishing split tiles) */
   int grid;          /* persistent CTAs                                        */
   int tiles;         /* N / 128                                                */
   int k_blocks;      /* ceil(K / k_per_stage): stages per output tile          */
   int smem_bytes;    /* dynamic shared memory per CTA                          */
   int passes;        /* ceil(M / 16) launches                                  */
   int math;          /* 0 = mma.sync tensor-core tiles, 1 = CUDA-core FMA (reserved) */
+  int pdl;           /* 1 = programmatic dependent launch: the kernel may start, and prefetch
+                        weight tiles, while the previous kernel of the stream drains; it reads
+                        activations and writes nothing before that kernel has completed       */
 } fg_plan_t;
 
 /* Pure host function (callable without a GPU): fills *out for a problem on a device
@@ -129,6 +132,16 @@ int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const v
 int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev,
                    void* C_host, void* x_stage_dev, void* C_stage_dev, int M, int N, int K,
                    void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* ---- built-in tracer -----------------------------------------------------------
+ * While enabled (process-wide), every launch records eight %globaltimer stamps (ns) per
+ * CTA in a spare corner of the workspace: [0] CTA start, [1] first copy issued, [2] last
+ * copy issued, [3] first stage landed, [4] warp 0 done with the last segment's math,
+ * [7] all warps done with it, [5] last segment flushed, [6] number of segments.
+ * fg_trace_read synchronises `stream`, copies 8*ctas values to `out` and clears them.
+ * Costs one predicated branch per event when disabled. */
+int fg_trace_enable(int on);
+int fg_trace_read(void* ws, unsigned long long* out, int ctas, fg_stream_t stream);
 
 /* ---- diagnostics -------------------------------------------------------------- */
 const char* fg_status_str(int status);

@@ -1,0 +1,124 @@
+"""The launch heuristic and the stream-K work split, on the CPU.
+
+`simulate` mirrors the kernel's index arithmetic (range of each CTA, its segments, who
+contributes to a split tile and in which workspace slot) and checks the invariants the
+device code relies on."""
+import ctypes
+
+import pytest
+
+from fastgate_b200 import capi
+
+B200 = dict(sm_count=148, smem_optin=232448)
+CHUNK_K = {0: 64, 1: 64, 2: 128}
+
+
+def _range_begin(c, total, grid):
+    return (c * total) // grid
+
+
+def _cta_of_unit(u, total, grid):
+    c = (u * grid) // total
+    while c + 1 < grid and _range_begin(c + 1, total, grid) <= u:
+        c += 1
+    while c > 0 and _range_begin(c, total, grid) > u:
+        c -= 1
+    return c
+
+
+def simulate(tiles, k_blocks, grid):
+    total = tiles * k_blocks
+    covered = [0] * total
+    contrib = {}
+    for c in range(grid):
+        ub, ue = _range_begin(c, total, grid), _range_begin(c + 1, total, grid)
+        assert ue > ub, "every CTA owns at least one unit"
+        u, partial_segments = ub, 0
+        while u < ue:
+            tile, kb0 = divmod(u, k_blocks)
+            ln = min(k_blocks - kb0, ue - u)
+            for i in range(u, u + ln):
+                covered[i] += 1
+            if ln != k_blocks:
+                partial_segments += 1
+                contrib.setdefault(tile, []).append((c, 0 if u == ub else 1))
+            u += ln
+        assert partial_segments <= 2, "two workspace slots per CTA must suffice"
+    assert all(v == 1 for v in covered), "each (tile, k-block) is streamed exactly once"
+    for tile, lst in contrib.items():
+        first = _cta_of_unit(tile * k_blocks, total, grid)
+        last = _cta_of_unit(tile * k_blocks + k_blocks - 1, total, grid)
+        want = [(c, 0 if _range_begin(c, total, grid) // k_blocks == tile else 1) for c in range(first, last + 1)]
+        assert lst == want, (tile, lst, want)
+        assert len(lst) >= 2
+    # imbalance: no CTA streams more than one stage more than another
+    sizes = [_range_begin(c + 1, total, grid) - _range_begin(c, total, grid) for c in range(grid)]
+    assert max(sizes) - min(sizes) <= 1
+    return contrib
+
+
+SHAPES = [(1, 16, 8192, 8192), (1, 1, 11008, 4096), (1, 1, 4096, 11008), (0, 8, 4096, 4096),
+          (2, 1, 28672, 8192), (2, 8, 28672, 8192), (1, 16, 9216, 3072), (1, 16, 3072, 3072),
+          (1, 16, 12288, 3072), (1, 16, 3072, 12288), (1, 4, 128, 128), (0, 3, 256, 384),
+          (1, 16, 1152, 3072), (1, 16, 384, 3072), (1, 16, 1536, 3072), (1, 33, 4096, 4096)]
+
+
+@pytest.mark.parametrize("op,M,N,K", SHAPES)
+def test_plan_invariants(op, M, N, K):
+    p = capi.plan(op, M, N, K, **B200)
+    assert p.op == op and p.tiles == N // 128
+    assert p.m_tile in (8, 16) and (p.m_tile == 16 or M <= 8)
+    assert p.k_per_stage % CHUNK_K[op] == 0
+    assert p.k_blocks == -(-K // p.k_per_stage)
+    assert 1 <= p.grid <= min(148, p.tiles * p.k_blocks)
+    assert p.stages >= 2 and p.stages % p.consumer_warps == 0, "a ring slot must always meet the same warp"
+    assert p.smem_bytes <= 232448
+    assert p.passes == -(-M // 16)
+    assert capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK
+    simulate(p.tiles, p.k_blocks, p.grid)
+
+
+@pytest.mark.parametrize("tiles,k_blocks,grid", [(86, 32, 148), (32, 86, 148), (64, 64, 148), (224, 32, 148),
+                                                 (1, 2, 2), (1, 1, 1), (3, 7, 5), (24, 48, 148), (9, 24, 148),
+                                                 (3, 24, 72), (7, 5, 35), (5, 3, 4), (86, 64, 132)])
+def test_streamk_split(tiles, k_blocks, grid):
+    simulate(tiles, k_blocks, grid)
+
+
+def test_plan_rejects_bad_problems():
+    p = capi.Plan()
+    L = capi.lib
+    assert L.fg_plan(1, 1, 100, 128, 0, 0, ctypes.byref(p)) == capi.FG_ERR_SHAPE
+    assert L.fg_plan(1, 1, 128, 100, 0, 0, ctypes.byref(p)) == capi.FG_ERR_SHAPE
+    assert L.fg_plan(1, 0, 128, 128, 0, 0, ctypes.byref(p)) == capi.FG_ERR_SHAPE
+    assert L.fg_plan(9, 1, 128, 128, 0, 0, ctypes.byref(p)) == capi.FG_ERR_PLAN
+    assert L.fg_plan(1, 1, 128, 128, 0, 0, None) == capi.FG_ERR_NULL
+
+
+def test_validate_catches_edited_plans():
+    L = capi.lib
+    good = capi.plan(1, 16, 8192, 8192, **B200)
+
+    def edited(**kw):
+        q = capi.Plan()
+        ctypes.memmove(ctypes.byref(q), ctypes.byref(good), ctypes.sizeof(q))
+        for k, v in kw.items():
+            setattr(q, k, v)
+        return L.fg_plan_validate(ctypes.byref(q), 8192, 8192, 232448)
+
+    assert edited() == capi.FG_OK
+    assert edited(stages=good.stages + 1) == capi.FG_ERR_PLAN      # smem no longer matches / not a multiple
+    assert edited(consumer_warps=9) == capi.FG_ERR_PLAN
+    assert edited(m_tile=12) == capi.FG_ERR_PLAN
+    assert edited(grid=0) == capi.FG_ERR_PLAN
+    assert edited(grid=100000) == capi.FG_ERR_PLAN
+    assert edited(k_blocks=good.k_blocks + 1) == capi.FG_ERR_PLAN
+    assert edited(tiles=good.tiles + 1) == capi.FG_ERR_PLAN
+    assert edited(k_per_stage=96) == capi.FG_ERR_PLAN
+    assert edited(smem_bytes=good.smem_bytes + 16) == capi.FG_ERR_PLAN
+
+
+def test_default_device_is_b200():
+    a = capi.plan(1, 8, 8192, 8192)          # 0/0 = B200 defaults
+    b = capi.plan(1, 8, 8192, 8192, **B200)
+    assert a.as_dict() == b.as_dict()
