@@ -39,9 +39,9 @@ if ROOT not in sys.path:
 
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 N_WEIGHT_COPIES = 4
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the M=16 case, from the ncu
-# capture summarised in profiles/ (None until one has been taken)
-NCU_TRAFFIC_BYTES_M16 = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch, mean over the five launches of one
+# step, from the ncu capture summarised in profiles/fg_streamk_kernel__bt_sweep__ncu_full.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 140.1e6
 
 
 def parse_args():
@@ -316,7 +316,7 @@ def run_ours(args):
         "no_gather": {"value": bytes_step_rank * world / ms_step_local / 1e6, "unit": "GB/s", "ms_per_step": ms_step_local},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
-                     "traffic": NCU_TRAFFIC_BYTES_M16, "kernel": "fg::fg_streamk_kernel<1,8|16>",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "fg::fg_streamk_kernel<1,8|16>",
                      "algorithmic_bytes_per_launch": avg_bytes},
         "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e,
     }
