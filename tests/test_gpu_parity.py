@@ -165,19 +165,18 @@ def test_int8_unscaled_reference_semantics(dev, ws):
 
 
 # ---- properties at full size --------------------------------------------------------------------
-def _half_ulps(a: torch.Tensor, b: torch.Tensor) -> int:
-    """Largest distance between two fp16 tensors, in units of the last place."""
-    def key(t):
-        i = t.view(torch.int16).to(torch.int32)
-        return torch.where(i < 0, -(i & 0x7FFF), i)
-    return int((key(a) - key(b)).abs().max())
+def _one_rounding_step_apart(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """True if two fp16 results of the same sums differ by no more than a last-place flip of
+    a value of magnitude >= 1 (a tenth of the path's tolerance): what a different fp32
+    summation order can do, and far less than any dropped or doubled term would."""
+    return oracle.tolerance_excess(gu.to_np(a), gu.to_np(b).astype(np.float32)) <= 0.1
 
 
 def test_linearity_and_row_independence(dev, ws):
     """Rows of x are independent.  With the same accumulator tile height a row's bits do not
     depend on which other rows travel with it or on the pass it lands in; across tile heights
     (another K split over the warps) only the fp32 summation order changes: at most one
-    unit in the last place of the fp16 result."""
+    rounding step of the fp16 result."""
     case = wl.Case("rows", wl.OP_NK, 40, 8192, 8192, 77)
     x, W, _ = inputs(case)
     xd, Wd = x.to(dev), W.to(dev)
@@ -190,7 +189,7 @@ def test_linearity_and_row_independence(dev, ws):
     for (a, b) in [(0, 1), (0, 8), (3, 4), (39, 40)]:  # 8-row tiles
         part = torch.zeros(b - a, 8192, dtype=torch.float16, device=dev)
         assert gu.call(wl.OP_NK, xd[a:b].contiguous(), Wd, None, part, b - a, 8192, 8192, ws) == capi.FG_OK
-        assert _half_ulps(part, full[a:b]) <= 1, (a, b)
+        assert _one_rounding_step_apart(part, full[a:b]), (a, b)
     one = torch.zeros(1, 8192, dtype=torch.float16, device=dev)
     eight = torch.zeros(8, 8192, dtype=torch.float16, device=dev)
     assert gu.call(wl.OP_NK, xd[2:3].contiguous(), Wd, None, one, 1, 8192, 8192, ws) == capi.FG_OK
@@ -219,7 +218,7 @@ def test_layouts_agree_bitwise(dev, ws):
 
 def test_n_shards_concatenate_to_the_full_result(dev, ws):
     """Column-partitioning the weight by N (the multi-GPU scheme) only moves the stream-K cuts,
-    i.e. the fp32 summation order: the assembled result is within one unit in the last place
+    i.e. the fp32 summation order: the assembled result is within one rounding step
     of the single-GPU one, and within tolerance of the oracle."""
     case = wl.Case("shards", wl.OP_NK, 16, 9216, 3072, 123)
     x, W, _ = inputs(case)
@@ -234,7 +233,7 @@ def test_n_shards_concatenate_to_the_full_result(dev, ws):
             assert gu.call(wl.OP_NK, xd, W[b:e].contiguous().to(dev), None, o, 16, e - b, 3072, ws) == capi.FG_OK
             parts.append(o)
         cat = torch.cat(parts, dim=1)
-        assert _half_ulps(cat, full) <= 1, world
+        assert _one_rounding_step_apart(cat, full), world
         oracle.check_tolerance(gu.to_np(cat), oracle.gemm_nk(x.numpy(), W.numpy()), f"{world} shards")
 
 
