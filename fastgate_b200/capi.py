@@ -19,7 +19,8 @@ FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK = 0, 1, 2
 # every symbol include/fastgate_b200.h declares
 EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
-    "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_planned", "fg_linear_host",
+    "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
+    "fg_linear_host",
     "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
@@ -51,6 +52,7 @@ def _load() -> ctypes.CDLL:
     L.fg_gemm_f16_kn.argtypes = [vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_f16_nk.argtypes = [vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_w8a16_nk.argtypes = [vp, vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_gemm_f16_nk_noalloc.argtypes = [vp, vp, vp, i, i, i, vp]
     L.fg_gemm_planned.argtypes = [ctypes.POINTER(Plan), vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_trace_enable.argtypes = [i]

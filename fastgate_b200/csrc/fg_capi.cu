@@ -219,6 +219,41 @@ int run_op(int op, const void* x, const void* W, const void* scales, void* C, in
   return run_planned(pl, dev, x, W, scales, C, M, N, K, ws, reinterpret_cast<cudaStream_t>(stream));
 }
 
+// ---- scratch for fg_gemm_f16_nk_noalloc -------------------------------------------------
+// Callers that must not (or cannot) call cudaMalloc -- code running inside someone else's
+// memory budget, a plugin that is handed buffers but no allocator, a latency-critical loop
+// that may not touch the allocator -- get the split-K scratch from this file-scope array
+// instead of a workspace.  Every GPU that loads the library carries it until the process
+// exits.  Layout: [0,256) status word | 4 B arrival counter per output tile | two fp32
+// partial tiles of 16 x 128 per persistent CTA.
+constexpr int kNoAllocMaxN = 65536;   // at most 512 output tiles
+constexpr int kNoAllocMaxGrid = 160;  // persistent CTAs (a B200 has 148 SMs)
+constexpr size_t kNoAllocTicketsOffset = 256;
+constexpr size_t kNoAllocPartialsOffset = kNoAllocTicketsOffset + 4 * (kNoAllocMaxN / 128);
+constexpr size_t kNoAllocBytes =
+    kNoAllocPartialsOffset + static_cast<size_t>(kNoAllocMaxGrid) * 2 * FG_WS_PARTIAL_TILE_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address;
+// the address is looked up once per device, with that device current.
+unsigned char* g_noalloc_ptr[kMaxDevices] = {};
+std::mutex g_noalloc_mu;
+
+int noalloc_scratch(int dev_index, unsigned char** out) {
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_ptr[dev_index] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    g_noalloc_ptr[dev_index] = static_cast<unsigned char*>(ptr);
+  }
+  *out = g_noalloc_ptr[dev_index];
+  return FG_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -326,6 +361,84 @@ int fg_trace_read(void* ws, unsigned long long* out, int ctas, fg_stream_t strea
   if (e != cudaSuccess) {
     g_last_cuda = static_cast<int>(e);
     return FG_ERR_CUDA;
+  }
+  return FG_OK;
+}
+
+int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, int K,
+                           fg_stream_t stream) {
+  if (x == nullptr || W == nullptr || C == nullptr) return FG_ERR_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || (N % 128) != 0 || (K % 128) != 0) return FG_ERR_SHAPE;
+  if (N > kNoAllocMaxN) return FG_ERR_WORKSPACE;  // more output tiles than the built-in scratch has counters for
+  if (!aligned16(x) || !aligned16(W) || !aligned16(C)) return FG_ERR_ALIGN;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != FG_OK) return st;
+  int dev_index = 0;
+  cudaError_t e = cudaGetDevice(&dev_index);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  unsigned char* scratch = nullptr;
+  if ((st = noalloc_scratch(dev_index, &scratch)) != FG_OK) return st;
+
+  fg_plan_t pl;
+  const int sms = dev->sm_count < kNoAllocMaxGrid ? dev->sm_count : kNoAllocMaxGrid;
+  if ((st = fg_plan(FG_OP_F16_NK, M, N, K, sms, dev->smem_optin, &pl)) != FG_OK) return st;
+  if (pl.grid > kNoAllocMaxGrid) return FG_ERR_WORKSPACE;
+  pl.pdl = 0;  // a memset precedes every launch, so there is no kernel to overlap with
+
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  KernelFn kern = pick_kernel(FG_OP_F16_NK, pl.m_tile);
+  int& set = dev->smem_set[FG_OP_F16_NK][pl.m_tile == 16];
+  if (pl.smem_bytes > set) {
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             pl.smem_bytes);
+    if (e != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    set = pl.smem_bytes;
+  }
+  CUtensorMap tmW;
+  if ((st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, W, K, N, 64, 128)) != FG_OK) return st;
+
+  fg::KParams p;
+  p.scales = nullptr;
+  p.status = reinterpret_cast<int*>(scratch);
+  p.tickets = reinterpret_cast<unsigned int*>(scratch + kNoAllocTicketsOffset);
+  p.partials = reinterpret_cast<float*>(scratch + kNoAllocPartialsOffset);
+  p.trace = nullptr;
+  p.N = N;
+  p.K = K;
+  p.tiles = pl.tiles;
+  p.k_blocks = pl.k_blocks;
+  p.chunks_per_stage = pl.k_per_stage / fg_chunk_k(FG_OP_F16_NK);
+  p.stages = pl.stages;
+  p.consumer_warps = pl.consumer_warps;
+  p.pdl = 0;
+  for (int m0 = 0; m0 < M; m0 += 16) {
+    const int mp = (M - m0) < 16 ? (M - m0) : 16;
+    // The array is shared by every call and keeps what the last one left: the status word
+    // and the arrival counters must read zero when the kernel starts.
+    e = cudaMemsetAsync(scratch, 0, kNoAllocPartialsOffset, s);
+    if (e != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    CUtensorMap tmX;
+    const __half* xp = static_cast<const __half*>(x) + static_cast<size_t>(m0) * K;
+    if ((st = encode_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xp, K, mp, 64, pl.m_tile)) != FG_OK) return st;
+    p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * N;
+    p.M = mp;
+    kern<<<pl.grid, (pl.consumer_warps + 2) * 32, pl.smem_bytes, s>>>(tmW, tmX, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
   }
   return FG_OK;
 }

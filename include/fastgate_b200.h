@@ -119,6 +119,24 @@ int fg_gemm_f16_nk(const void* x, const void* W, void* C, int M, int N, int K,
 int fg_gemm_w8a16_nk(const void* x, const int8_t* W8, const void* scales, void* C,
                      int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream);
 
+/* Same operation as fg_gemm_f16_nk for callers that cannot allocate device memory: a
+ * plugin that is handed its buffers and nothing else, code running under a fixed memory
+ * budget, a loop that may not enter the allocator.  It takes no workspace: the split-K
+ * scratch (arrival counters and fp32 partial tiles, about 2.5 MB) is a static array inside
+ * the library, present on every GPU that loads it until the process exits, and the call
+ * itself allocates nothing (no cudaMalloc/cudaFree, no allocating library routine).
+ *   - Limits: N <= 65536 and at most 160 persistent CTAs; beyond that FG_ERR_WORKSPACE.
+ *   - The first call on a device looks up the array's device address; make that call
+ *     before any stream capture involving this entry point.
+ *   - All calls share the one array.  Each call first clears the status word and the
+ *     counters on `stream`, so calls are correct back to back on one stream; calls that
+ *     may overlap on the GPU (different streams, different host threads) race on it and
+ *     must be serialised by the caller.
+ * It has no counterpart in the reference, whose launchers allocate nothing and use
+ * fp16 atomics on C instead of scratch (backend/cuda/hk/edgemm.cu:138-142). */
+int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, int K,
+                           fg_stream_t stream);
+
 /* Same three operations with an explicit plan (from fg_plan, possibly edited):
  * used by the tuner and the tests that walk every plan the heuristic can emit. */
 int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const void* scales,
