@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--no-graph", action="store_true", help="launch on a stream instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-push", action="store_true", help="N > 1: assemble outputs with NCCL only")
     ap.add_argument("--reference-arm", choices=("auto", "gpu", "cpu"), default="auto")
     return ap.parse_args()
 
@@ -124,6 +125,7 @@ def dist_setup(args):
             raise SystemExit("bench.py --gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")  # keep NCCL's version banner off stdout
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     return world, rank, local
 
@@ -222,6 +224,19 @@ def run_ours(args):
             layers[(state["i"] + ci) % N_WEIGHT_COPIES].forward(xs[ci])
         state["i"] += 1
 
+    def step_push():
+        # The five calls are chained the way the layers of a model are: call i+1 reads its
+        # activations only after every rank's tiles of call i have landed here (a wait inside
+        # the kernel, after its first weight tiles are already on their way); one wait kernel
+        # closes the step, so all five outputs are complete on every rank when the step ends.
+        prev = None
+        for ci in range(len(cases)):
+            lay = layers[(state["i"] + ci) % N_WEIGHT_COPIES]
+            lay.forward_push(xs[ci], wait=False, after=prev)
+            prev = lay.last_push(cases[ci].M)
+        lay.push_wait(prev)
+        state["i"] += 1
+
     # ---- device-resident timing -------------------------------------------------------
     graph = None
     use_graph = (not args.no_graph) and world == 1
@@ -246,8 +261,20 @@ def run_ours(args):
     else:
         ms_local = time_steps(step_local, args.steps, args.warmup, world, stream)
         launches = fg.launch_count() - launches0 - args.warmup * len(cases)
+    ms_nccl = None
+    gather_kind = "none (single GPU)"
     if world > 1:
-        ms_full = time_steps(step_gather, args.steps, args.warmup, world, stream)
+        ms_nccl = time_steps(step_gather, args.steps, args.warmup, world, stream)
+        ms_full, gather_kind = ms_nccl, "NCCL all_gather_into_tensor + [g,M,N/g]->[M,N] copy per call"
+        if not args.no_push:
+            try:
+                with torch.cuda.stream(stream):
+                    step_push()  # collective: allocates and exchanges the symmetric outputs
+                    torch.cuda.synchronize()
+                ms_full = time_steps(step_push, args.steps, args.warmup, world, stream)
+                gather_kind = "fused: epilogue stores tiles into every rank's C over NVLink + bounded flag wait"
+            except Exception as e:  # symmetric memory unavailable: keep the NCCL number
+                sys.stderr.write(f"rank {rank}: fused all-gather unavailable ({e}); reporting the NCCL path\n")
     else:
         ms_full = ms_local
     clocks = sampler.stop() if sampler else None
@@ -278,15 +305,35 @@ def run_ours(args):
         outs_host = [torch.empty(c.M, c.N, dtype=torch.float16).pin_memory() for c in cases]
         x_stage = [torch.empty_like(x) for x in xs]
 
+        use_push = world > 1 and gather_kind.startswith("fused")
+
+        # single GPU: the step's five activations travel as one pinned block, the five
+        # results come back as one block (one copy each way per step)
+        rows = [0]
+        for c in cases:
+            rows.append(rows[-1] + c.M)
+        x_all_host = torch.cat(xs_host).pin_memory()
+        x_all_dev = torch.empty_like(x_all_host, device=dev)
+        out_all_dev = torch.empty(rows[-1], cases[0].N, dtype=torch.float16, device=dev)
+        out_all_host = torch.empty(rows[-1], cases[0].N, dtype=torch.float16).pin_memory()
+
         def step_e2e():
-            for ci in range(len(cases)):
-                x_stage[ci].copy_(xs_host[ci], non_blocking=True)
-                lay = layers[(state["i"] + ci) % N_WEIGHT_COPIES]
-                out = lay.forward(x_stage[ci]) if world > 1 else lay.forward_local(x_stage[ci])
-                if rank == 0 or world == 1:
-                    outs_host[ci].copy_(out[:, :cases[ci].N] if world > 1 else out, non_blocking=True)
+            if world == 1:
+                x_all_dev.copy_(x_all_host, non_blocking=True)
+                for ci in range(len(cases)):
+                    fg.edgemm_m8n128k64x4_bt(x_all_dev[rows[ci]:rows[ci + 1]], weights[(state["i"] + ci) % N_WEIGHT_COPIES],
+                                             out_all_dev[rows[ci]:rows[ci + 1]])
+                out_all_host.copy_(out_all_dev, non_blocking=True)
+            else:
+                for ci in range(len(cases)):
+                    x_stage[ci].copy_(xs_host[ci], non_blocking=True)
+                for ci in range(len(cases)):
+                    lay = layers[(state["i"] + ci) % N_WEIGHT_COPIES]
+                    res = lay.forward_push(x_stage[ci]) if use_push else lay.forward(x_stage[ci])
+                    # the next call may reuse the layer's output buffer: read it out now
+                    outs_host[ci].copy_(res[:, :cases[ci].N], non_blocking=True)
             state["i"] += 1
-            torch.cuda.current_stream().synchronize()  # the caller has its result
+            torch.cuda.current_stream().synchronize()  # the caller has its results
 
         ms_e2e = time_steps(step_e2e, args.steps, args.warmup, world, stream)
         e2e = {"value": bytes_step_rank * world / (ms_e2e / args.steps) / 1e6, "unit": "GB/s",
@@ -310,10 +357,12 @@ def run_ours(args):
         "config": {"workload": "bt_sweep: edgemm_m8n128k64x4_bt, M in {1,2,4,8,16}, K=N=8192 per GPU, weight NxK fp16",
                    "calls_per_step": len(cases), "l2": f"{N_WEIGHT_COPIES} rotating weight copies (537 MB) > 126 MB L2",
                    "launch": "cuda graph replay" if graph is not None else "stream launches",
-                   "sharding": f"N-sharded, {world} x 8192 columns, NCCL all-gather per call" if world > 1 else "single GPU"},
+                   "sharding": f"N-sharded, {world} x 8192 columns; gather: {gather_kind}" if world > 1 else "single GPU"},
         "us_per_call": ms_step * 1e3 / len(cases),
         "per_call": per_call,
         "no_gather": {"value": bytes_step_rank * world / ms_step_local / 1e6, "unit": "GB/s", "ms_per_step": ms_step_local},
+        "nccl_gather": None if ms_nccl is None else {"value": bytes_step_rank * world / (ms_nccl / args.steps) / 1e6,
+                                                     "unit": "GB/s", "ms_per_step": ms_nccl / args.steps},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "fg::fg_streamk_kernel<1,8|16>",
@@ -386,11 +435,20 @@ def run_reference(args):
             ref.edgemm_m8n128k64x4_bt(xs[ci], weights[(state["i"] + ci) % N_WEIGHT_COPIES], outs[ci])
         state["i"] += 1
 
-    def step_e2e():
+    rows = [0]
+    for c in cases:
+        rows.append(rows[-1] + c.M)
+    x_all_host = torch.cat(xs_host).pin_memory()
+    x_all_dev = torch.empty_like(x_all_host, device=dev)
+    out_all_dev = torch.zeros(rows[-1], cases[0].N, dtype=torch.float16, device=dev)
+    out_all_host = torch.empty(rows[-1], cases[0].N, dtype=torch.float16).pin_memory()
+
+    def step_e2e():  # same shape as our arm: one block in, five operator calls, one block out
+        x_all_dev.copy_(x_all_host, non_blocking=True)
         for ci in range(len(cases)):
-            x_stage[ci].copy_(xs_host[ci], non_blocking=True)
-            ref.edgemm_m8n128k64x4_bt(x_stage[ci], weights[(state["i"] + ci) % N_WEIGHT_COPIES], outs[ci])
-            outs_host[ci].copy_(outs[ci], non_blocking=True)
+            ref.edgemm_m8n128k64x4_bt(x_all_dev[rows[ci]:rows[ci + 1]], weights[(state["i"] + ci) % N_WEIGHT_COPIES],
+                                      out_all_dev[rows[ci]:rows[ci + 1]])
+        out_all_host.copy_(out_all_dev, non_blocking=True)
         state["i"] += 1
         stream.synchronize()
 

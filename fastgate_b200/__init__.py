@@ -11,15 +11,21 @@ There is no CPU path and no fallback: importing this package needs the built ext
 """
 import torch as _torch  # noqa: F401  (loads libtorch before the extension)
 
+__version__ = "0.1"
+
 try:
     from . import _C
-except ImportError as e:  # pragma: no cover - exercised only on a broken install
-    raise ImportError(
-        "fastgate_b200: the native extension fastgate_b200/_C.so is missing or unloadable; "
-        "run `python -m fastgate_b200.build` (there is no CPU fallback)") from e
+    from .ops import *  # noqa: F401,F403
+    from .ops import __all__ as _ops_all
 
-from .ops import *  # noqa: F401,F403
-from .ops import __all__ as _ops_all
+    __all__ = list(_ops_all)
+except (ImportError, AttributeError) as _e:  # missing or stale build
+    _import_error = _e
+    __all__ = []
 
-__all__ = list(_ops_all)
-__version__ = "0.1"
+    def __getattr__(name):
+        # Submodules that need no native code (build, workloads) stay importable so that the
+        # extension can be (re)built; every operator fails loudly.
+        raise ImportError(
+            f"fastgate_b200.{name}: the native extension fastgate_b200/_C.so is missing, unloadable or older than "
+            "the Python package; run `python -m fastgate_b200.build` (there is no CPU fallback)") from _import_error

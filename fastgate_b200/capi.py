@@ -20,7 +20,7 @@ FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK = 0, 1, 2
 EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
     "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
-    "fg_linear_host",
+    "fg_gemm_f16_nk_push", "fg_push_wait", "fg_linear_host",
     "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
@@ -34,6 +34,14 @@ class Plan(ctypes.Structure):
 
     def as_dict(self) -> dict:
         return {n: getattr(self, n) for n, _ in self._fields_}
+
+
+class Peers(ctypes.Structure):
+    """Mirror of fg_peers_t."""
+
+    _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("n_total", ctypes.c_longlong),
+                ("C", ctypes.c_void_p * 8), ("flag", ctypes.c_void_p * 8),
+                ("wait_flags", ctypes.c_void_p), ("wait_target", ctypes.c_ulonglong)]
 
 
 def _load() -> ctypes.CDLL:
@@ -54,6 +62,8 @@ def _load() -> ctypes.CDLL:
     L.fg_gemm_w8a16_nk.argtypes = [vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_f16_nk_noalloc.argtypes = [vp, vp, vp, i, i, i, vp]
     L.fg_gemm_planned.argtypes = [ctypes.POINTER(Plan), vp, vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_gemm_f16_nk_push.argtypes = [vp, vp, i, i, i, ctypes.POINTER(Peers), vp, sz, vp]
+    L.fg_push_wait.argtypes = [vp, i, ctypes.c_ulonglong, vp, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_trace_enable.argtypes = [i]
     L.fg_trace_read.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong), i, vp]

@@ -133,7 +133,8 @@ int check_common(const void* x, const void* W, const void* C, int M, int N, int 
 }
 
 int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
-                const void* scales, void* C, int M, int N, int K, void* ws, cudaStream_t stream) {
+                const void* scales, void* C, int M, int N, int K, void* ws, cudaStream_t stream,
+                const fg_peers_t* peers = nullptr) {
   const int op = pl.op;
   const int chunks = pl.k_per_stage / fg_chunk_k(op);
   KernelFn kern = pick_kernel(op, pl.m_tile);
@@ -176,6 +177,26 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.stages = pl.stages;
   p.consumer_warps = pl.consumer_warps;
   p.pdl = pl.pdl ? 1 : 0;
+  p.world = 0;
+  p.rank = 0;
+  p.col0 = 0;
+  p.ldc = N;
+  p.wait_flags = nullptr;
+  p.wait_world = 0;
+  p.wait_target = 0;
+  if (peers != nullptr) {
+    p.wait_flags = peers->wait_flags;
+    p.wait_world = peers->world;
+    p.wait_target = peers->wait_target;
+    p.world = peers->world;
+    p.rank = peers->rank;
+    p.col0 = peers->rank * N;
+    p.ldc = peers->n_total;
+    for (int q = 0; q < peers->world; ++q) {
+      p.peer_C[q] = static_cast<__half*>(peers->C[q]);
+      p.peer_flag[q] = peers->flag[q];
+    }
+  }
 
   for (int m0 = 0; m0 < M; m0 += 16) {
     const int mp = (M - m0) < 16 ? (M - m0) : 16;
@@ -186,6 +207,9 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     if (st != FG_OK) return st;
     p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * N;
     p.M = mp;
+    if (peers != nullptr)
+      for (int q = 0; q < peers->world; ++q)
+        p.peer_C[q] = static_cast<__half*>(peers->C[q]) + static_cast<size_t>(m0) * peers->n_total;
     // consumer warps + one copy-issuing warp + one warp that finishes split tiles
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.grid);
@@ -317,6 +341,42 @@ int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const v
                      reinterpret_cast<cudaStream_t>(stream));
 }
 
+int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, int K,
+                        const fg_peers_t* peers, void* ws, size_t ws_bytes, fg_stream_t stream) {
+  if (peers == nullptr) return FG_ERR_NULL;
+  if (peers->world < 1 || peers->world > fg::kMaxPeers || peers->rank < 0 || peers->rank >= peers->world)
+    return FG_ERR_PLAN;
+  if (peers->n_total != static_cast<long long>(peers->world) * N_local) return FG_ERR_SHAPE;
+  for (int q = 0; q < peers->world; ++q) {
+    if (peers->C[q] == nullptr || peers->flag[q] == nullptr) return FG_ERR_NULL;
+    if (!aligned16(peers->C[q]) || (reinterpret_cast<uintptr_t>(peers->flag[q]) & 7u) != 0) return FG_ERR_ALIGN;
+  }
+  if ((reinterpret_cast<uintptr_t>(peers->wait_flags) & 7u) != 0) return FG_ERR_ALIGN;
+  int st = check_common(x, W_shard, peers->C[peers->rank], M, N_local, K, ws, ws_bytes);
+  if (st != FG_OK) return st;
+  DeviceInfo* dev = nullptr;
+  if ((st = device_info(&dev)) != FG_OK) return st;
+  fg_plan_t pl;
+  if ((st = fg_plan(FG_OP_F16_NK, M, N_local, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+  return run_planned(pl, dev, x, W_shard, nullptr, peers->C[peers->rank], M, N_local, K, ws,
+                     reinterpret_cast<cudaStream_t>(stream), peers);
+}
+
+int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long long target, void* ws,
+                 fg_stream_t stream) {
+  if (my_flags == nullptr || ws == nullptr) return FG_ERR_NULL;
+  if (world < 1 || world > fg::kMaxPeers) return FG_ERR_PLAN;
+  fg::fg_push_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(my_flags, world, target,
+                                                                              static_cast<int*>(ws));
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
 int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev, void* C_host,
                    void* x_stage_dev, void* C_stage_dev, int M, int N, int K, void* ws,
                    size_t ws_bytes, fg_stream_t stream) {
@@ -418,6 +478,13 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   p.stages = pl.stages;
   p.consumer_warps = pl.consumer_warps;
   p.pdl = 0;
+  p.world = 0;
+  p.rank = 0;
+  p.col0 = 0;
+  p.ldc = N;
+  p.wait_flags = nullptr;
+  p.wait_world = 0;
+  p.wait_target = 0;
   for (int m0 = 0; m0 < M; m0 += 16) {
     const int mp = (M - m0) < 16 ? (M - m0) : 16;
     // The array is shared by every call and keeps what the last one left: the status word

@@ -39,6 +39,7 @@ constexpr int kTileN = 128;           // output columns per tile
 constexpr int kRedStride = 132;       // floats per row of the cross-warp reduction buffer
 constexpr int kChunkWBytes = 16384;   // weight bytes per chunk (128 columns x 128 B, or 64 k x 256 B)
 constexpr int kMaxConsumerWarps = 8;
+constexpr int kMaxPeers = 8;          // ranks of one NVLink box
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then give up
 
 enum { kOpF16KN = 0, kOpF16NK = 1, kOpW8A16NK = 2 };
@@ -76,6 +77,20 @@ struct KParams {
   int stages;
   int consumer_warps;
   int pdl;                   // 1: launched with programmatic stream serialization
+  // Fused all-gather ("push") of an N-sharded layer: when world > 0 the output tile is stored
+  // into the full [M, ldc] output of every rank at column col0 + n, and each finished tile
+  // bumps every rank's arrival counter.  Plain stores and atomics over NVLink peer mappings.
+  int world;                 // 0: plain local output
+  int rank;                  // this rank; it bumps counter [rank] of every rank's flag array
+  int col0;                  // first column of this rank's slice in the full output
+  long long ldc;             // row length of the full output
+  __half* peer_C[kMaxPeers];
+  unsigned long long* peer_flag[kMaxPeers];
+  // Optional dependency on an earlier pushed layer: the activations are only read once the
+  // `wait_world` per-source counters at wait_flags have reached wait_target (nullptr: none).
+  const unsigned long long* wait_flags;
+  int wait_world;
+  unsigned long long wait_target;
 };
 
 __host__ __device__ constexpr int chunk_bytes(int op, int mt) {
@@ -230,7 +245,37 @@ __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float
     v.x *= sc.x;
     v.y *= sc.y;
   }
-  *reinterpret_cast<__half2*>(p.C + static_cast<size_t>(m) * p.N + n) = __floats2half2_rn(v.x, v.y);
+  const __half2 h = __floats2half2_rn(v.x, v.y);
+  if (p.world == 0) {
+    *reinterpret_cast<__half2*>(p.C + static_cast<size_t>(m) * p.N + n) = h;
+  } else {
+    const size_t off = static_cast<size_t>(m) * p.ldc + p.col0 + n;
+    for (int q = 0; q < p.world; ++q) *reinterpret_cast<__half2*>(p.peer_C[q] + off) = h;
+  }
+}
+
+// One thread tells every rank that one more output tile of this rank has been delivered.
+// The callers make the tile's stores visible system-wide first (fence + barrier).
+__device__ __forceinline__ void signal_tile_delivered(const KParams& p) {
+  for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.rank, 1ull);
+}
+
+// Bounded wait until the first `world` per-source arrival counters at `flags` have all reached
+// `target`.  One counter per source rank: a fast rank that is already pushing its next call
+// cannot stand in for a slow one.
+__device__ __forceinline__ bool wait_counters(const unsigned long long* flags, int world,
+                                              unsigned long long target) {
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (int src = 0; src < world; ++src) {
+    for (;;) {
+      unsigned long long v;
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + src) : "memory");
+      if (v >= target) break;
+      if ((++spins & 0xffu) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) return false;
+    }
+  }
+  return true;
 }
 
 // Warp roles: [0, ncw) consume, ncw produces (TMA), ncw + 1 finishes split tiles.
@@ -325,14 +370,15 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
         }
       };
 
-      int it = 0;
-      if (p.pdl) {
-        // Programmatic dependent launch: this grid may start while the previous kernel of
-        // the stream is still draining.  The weight never depends on that kernel, so the
-        // first ring-full of weight tiles is requested right away; activations (which may be
-        // the previous kernel's output) only after griddepcontrol.wait.
-        griddep_launch_dependents();
-        const int pre = n_it < S ? n_it : S;
+      // The weight never depends on earlier kernels, so the first ring-full of weight tiles is
+      // requested right away.  Activations may be the output of the previous kernel of the
+      // stream (programmatic dependent launch: this grid may have started while that kernel
+      // was still draining) or of a layer that other ranks are still pushing, so they are
+      // only read after griddepcontrol.wait (a no-op for an ordinary launch) and, if asked,
+      // after the arrival counters of that layer have reached their target.
+      griddep_launch_dependents();
+      const int pre = n_it < S ? n_it : S;
+      {
         int t2 = tile, k2 = kb;
         for (int i = 0; i < pre; ++i) {
           const int nch = stage_chunks(k2);
@@ -340,14 +386,19 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
           issue_w(i, t2, k2, nch);
           if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
         }
-        griddep_wait();
-        for (int i = 0; i < pre; ++i) {
-          issue_x(i, kb, stage_chunks(kb));
-          if (++kb == static_cast<int>(KB)) { kb = 0; ++tile; }
-        }
-        it = pre;
-        issued = pre;
       }
+      griddep_wait();
+      if (p.wait_flags != nullptr && !wait_counters(p.wait_flags, p.wait_world, p.wait_target)) {
+        // The activations never became ready.  Complete the armed stages with what is there
+        // so that no copy is left in flight; the status word tells the caller.
+        atomicExch(p.status, kStatusTimeout);
+      }
+      for (int i = 0; i < pre; ++i) {
+        issue_x(i, kb, stage_chunks(kb));
+        if (++kb == static_cast<int>(KB)) { kb = 0; ++tile; }
+      }
+      int it = pre;
+      issued = pre;
       for (; it < n_it; ++it) {
         const int s = it % S;
         const uint32_t use = it / S;
@@ -452,6 +503,11 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
               }
             }
             if (lane == 0) p.tickets[tile] = 0;  // ready for the next launch
+            if (p.world > 0) {
+              __threadfence_system();
+              __syncwarp();
+              if (lane == 0) signal_tile_delivered(p);
+            }
           }
         }
         __syncwarp();
@@ -556,13 +612,25 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
     if (!whole) {
       mbar_arrive(bar_flush);  // release: this thread's share of the partial tile is stored
       ++ev;
+    } else if (p.world > 0) {
+      __threadfence_system();  // this thread's stores into the other ranks' outputs
     }
     named_bar_sync(1, nct);  // `red` is free again
+    if (whole && p.world > 0 && ctid == 0) signal_tile_delivered(p);
     if (trace && ctid == 0) trace[6] += 1;  // segments of this CTA
 
     u += len;
     it0 += len;
   }
+}
+
+// Waits (bounded) until each of the `world` per-source arrival counters of this rank has
+// reached `target`, i.e. until every rank has delivered all its tiles of the calls enqueued so
+// far.  One thread; ordered on the stream, so whatever follows it sees the complete output.
+__global__ void fg_push_wait_kernel(const unsigned long long* flags, int world, unsigned long long target,
+                                    int* status) {
+  if (threadIdx.x != 0) return;
+  if (!wait_counters(flags, world, target)) atomicExch(status, kStatusTimeout);
 }
 
 }  // namespace fg

@@ -16,6 +16,7 @@
 #include <stdexcept>
 #include <string>
 #include <utility>
+#include <vector>
 
 #include "../../include/fastgate_b200.h"
 
@@ -117,6 +118,65 @@ void op_wfirst_int8(at::Tensor W8, at::Tensor x, at::Tensor C, c10::optional<at:
   linear(FG_OP_W8A16_NK, x, W8, C, scales);
 }
 
+// ---- N-sharded layer with the all-gather fused into the epilogue --------------------------
+// x[M,K] fp16 (replicated), W[N_local,K] fp16 (this rank's rows); c_ptrs / flag_ptrs are the
+// device addresses, as mapped into this process, of every rank's full output [M, n_total]
+// and arrival counter (e.g. buffer_ptrs of a torch symmetric-memory allocation).
+void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std::vector<int64_t> flag_ptrs,
+                    int64_t rank, int64_t n_total, int64_t wait_flag_ptr, int64_t wait_target) {
+  check_tensor(x, "activation", at::kHalf);
+  check_tensor(W, "weight", at::kHalf);
+  if (x.dim() != 2 || W.dim() != 2 || x.size(1) != W.size(1))
+    throw std::runtime_error("fastgate_b200: activation [M,K] and weight [N_local,K] expected");
+  if (c_ptrs.size() != flag_ptrs.size() || c_ptrs.empty() || c_ptrs.size() > 8)
+    throw std::runtime_error("fastgate_b200: 1..8 peers expected");
+  const int64_t M = x.size(0), K = x.size(1), N = W.size(0);
+  if (M == 0) return;
+  if ((N % 128) != 0 || (K % 128) != 0) raise(FG_ERR_SHAPE, true);
+  fg_peers_t peers;
+  peers.world = static_cast<int>(c_ptrs.size());
+  peers.rank = static_cast<int>(rank);
+  peers.n_total = n_total;
+  peers.wait_flags = reinterpret_cast<const unsigned long long*>(wait_flag_ptr);
+  peers.wait_target = static_cast<unsigned long long>(wait_target);
+  for (size_t q = 0; q < c_ptrs.size(); ++q) {
+    peers.C[q] = reinterpret_cast<void*>(c_ptrs[q]);
+    peers.flag[q] = reinterpret_cast<unsigned long long*>(flag_ptrs[q]);
+  }
+  const c10::cuda::CUDAGuard guard(x.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
+  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  int st;
+  {
+    pybind11::gil_scoped_release nogil;
+    st = fg_gemm_f16_nk_push(x.data_ptr(), W.data_ptr(), M, N, K, &peers, ws.buf.data_ptr(), ws.bytes,
+                             reinterpret_cast<fg_stream_t>(stream));
+  }
+  if (st != FG_OK) raise(st, true);
+}
+
+// Enqueues the bounded wait for this rank's arrival counter on the current stream.
+void push_wait(int64_t flag_ptr, int64_t world, int64_t target, int64_t device) {
+  const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(device).stream();
+  Workspace& ws = workspace_for(static_cast<int>(device), stream, 128);
+  const int st = fg_push_wait(reinterpret_cast<const unsigned long long*>(flag_ptr), static_cast<int>(world),
+                              static_cast<unsigned long long>(target), ws.buf.data_ptr(),
+                              reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+}
+
+// Device status word of the current stream's workspace (synchronises the stream).
+int64_t workspace_status(int64_t device) {
+  const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(device).stream();
+  Workspace& ws = workspace_for(static_cast<int>(device), stream, 128);
+  int v = -1;
+  const int st = fg_workspace_status(ws.buf.data_ptr(), &v, reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+  return v;
+}
+
 // cuBLAS comparators of the reference (backend/cuda/hk/hgemm.cu:29-74, hgemm_tr.cu:30-75):
 // library calls, kept only so that scripts which import them keep working.
 void hgemm(at::Tensor A, at::Tensor B, at::Tensor C) {
@@ -159,6 +219,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         "as the reference launches it (backend/cuda/hk/fastgemv.cu:50-59)");
   m.def("hgemm", &hgemm);
   m.def("hgemm_tr", &hgemm_tr);
+  m.def("linear_nk_push", &linear_nk_push, py::arg("x"), py::arg("W"), py::arg("c_ptrs"), py::arg("flag_ptrs"),
+        py::arg("rank"), py::arg("n_total"), py::arg("wait_flag_ptr") = 0, py::arg("wait_target") = 0);
+  m.def("push_wait", &push_wait, py::arg("flag_ptr"), py::arg("world"), py::arg("target"), py::arg("device"));
+  m.def("workspace_status", &workspace_status, py::arg("device"));
   m.def("launch_count", []() { return fg_launch_count(); });
   m.def("version", []() { return std::string(fg_version()); });
 }

@@ -30,9 +30,11 @@ BZ_OPS = (
 )
 COMPARATORS = ("hgemm", "hgemm_tr")
 
-__all__ = list(KN_OPS + NK_OPS + WF_OPS + COMPARATORS) + ["launch_count", "version",
+EXTRA = ("linear_nk_push", "push_wait", "workspace_status")
+
+__all__ = list(KN_OPS + NK_OPS + WF_OPS + COMPARATORS + EXTRA) + ["launch_count", "version",
                                                          "KN_OPS", "NK_OPS", "WF_OPS", "BZ_OPS"]
 
-for _n in KN_OPS + NK_OPS + WF_OPS + COMPARATORS + ("launch_count", "version"):
+for _n in KN_OPS + NK_OPS + WF_OPS + COMPARATORS + EXTRA + ("launch_count", "version"):
     globals()[_n] = getattr(_C, _n)
 del _n

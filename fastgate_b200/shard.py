@@ -9,6 +9,12 @@ path; this is the column-parallel scheme its README's "t2vi inference" linears c
 
 Every shard keeps the kernels' contract (N/g % 128 == 0).  The gather delivers
 ``[g, M, N/g]``; ``assemble`` turns that into row-major ``[M, N]`` with one small copy.
+
+``forward_push`` is the fused alternative: the kernel's epilogue stores every finished
+128-column tile directly into the full ``C[M, N]`` of every rank through NVLink peer
+mappings (torch symmetric memory) and bumps each rank's arrival counter; a one-thread wait
+kernel then holds the stream until all ranks' tiles have landed.  No NCCL call, no
+``[g,M,N/g] -> [M,N]`` copy.  Plain peer stores only (no multimem, no TMA from peer memory).
 """
 from __future__ import annotations
 
@@ -27,6 +33,37 @@ def _default_compute(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, scales
         ops.fastgemv_int8(w, x, out, scales)
     else:
         ops.edgemm_m8n128k64x4_bt(x, w, out)
+
+
+class PushBuffers:
+    """The full output ``[m_max, n_total]`` of one layer and an arrival counter, allocated in
+    symmetric memory and exchanged with the other ranks of `group` (a collective call: every
+    rank must create its PushBuffers in the same order)."""
+
+    def __init__(self, m_max: int, n_total: int, device, group=None):
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device)
+        self.n_total = n_total
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            grp = group if group is not None else dist.group.WORLD
+            self.out = symm_mem.empty((m_max, n_total), dtype=torch.float16, device=self.device)
+            self.flag = symm_mem.empty((16,), dtype=torch.int64, device=self.device)
+            self.flag.zero_()
+            torch.cuda.synchronize(self.device)
+            self._h_out = symm_mem.rendezvous(self.out, grp)
+            self._h_flag = symm_mem.rendezvous(self.flag, grp)
+            self.c_ptrs = [int(p) for p in self._h_out.buffer_ptrs]
+            self.flag_ptrs = [int(p) for p in self._h_flag.buffer_ptrs]
+            dist.barrier(group)  # every counter is zero before anyone pushes
+        else:
+            self.out = torch.empty(m_max, n_total, dtype=torch.float16, device=self.device)
+            self.flag = torch.zeros(16, dtype=torch.int64, device=self.device)
+            self.c_ptrs = [self.out.data_ptr()]
+            self.flag_ptrs = [self.flag.data_ptr()]
+        self.target = 0  # tiles EACH rank will have delivered to this rank after the calls so far
 
 
 class ShardedLinear:
@@ -82,6 +119,44 @@ class ShardedLinear:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Full C[M, N] on every rank."""
         return self.assemble(self.gather(self.forward_local(x)))
+
+    # ---- fused all-gather -----------------------------------------------------------------
+    def push_buffers(self, m_max: int, device) -> "PushBuffers":
+        """Collective: allocate (once per m_max) the symmetric output of this layer."""
+        key = ("push", m_max)
+        if key not in self._bufs:
+            self._bufs[key] = PushBuffers(m_max, self.n_total, device, self.group)
+        return self._bufs[key]
+
+    def forward_push(self, x: torch.Tensor, wait: bool = True, after: Optional["PushBuffers"] = None) -> torch.Tensor:
+        """Full C[M, N] on every rank with the all-gather fused into the kernel's epilogue.
+
+        wait=False: the caller makes sure the result is complete before touching it, either
+        with `push_wait` or by handing this layer's buffers as `after=` to the next layer.
+        after=: x is the pushed output of that earlier layer; the kernel streams its first
+        weight tiles at once and reads x only when every rank's tiles of that layer have landed.
+        """
+        from . import ops
+
+        if self.w.dtype != torch.float16:
+            raise NotImplementedError("the fused all-gather is implemented for fp16 NxK weights")
+        M = x.shape[0]
+        pb = self.push_buffers(max(M, 16), x.device)
+        wait_ptr, wait_target = (after.flag_ptrs[after.rank], after.target) if after is not None else (0, 0)
+        ops.linear_nk_push(x, self.w, pb.c_ptrs, pb.flag_ptrs, pb.rank, self.n_total, wait_ptr, wait_target)
+        pb.target += (self.w.shape[0] // 128) * ((M + 15) // 16)
+        if wait:
+            self.push_wait(pb)
+        return pb.out[:M]
+
+    def last_push(self, M: int) -> "PushBuffers":
+        """The buffers the last forward_push with M rows wrote (to hand on as `after=`)."""
+        return self._bufs[("push", max(M, 16))]
+
+    def push_wait(self, pb: "PushBuffers") -> None:
+        from . import ops
+
+        ops.push_wait(pb.flag_ptrs[pb.rank], pb.world, pb.target, pb.device.index if pb.device.index is not None else 0)
 
 
 def shard_weight(weight: torch.Tensor, world: int, rank: int) -> torch.Tensor:

@@ -142,6 +142,37 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
 int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const void* scales,
                     void* C, int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream);
 
+/* ---- N-sharded layers over the GPUs of one box: fused all-gather ("push") --------------
+ * The reference has no multi-GPU path.  Rank r of `world` holds rows [r*N_local,
+ * (r+1)*N_local) of an NxK weight and computes C[:, r*N_local : (r+1)*N_local].  Instead of
+ * a separate all-gather, the kernel's epilogue stores each finished 128-column tile straight
+ * into the full output C[M, n_total] of EVERY rank (plain stores through NVLink peer
+ * mappings: symmetric memory, CUDA IPC or cudaDeviceEnablePeerAccess) and then adds 1 to
+ * counter [rank] of every rank's flag array (eight 64-bit counters, one per source rank).
+ * A call by rank r adds N_local/128 * ceil(M/16) to counter [r] on every rank;
+ * fg_push_wait enqueues a one-thread kernel that waits, for at most 2 s, until counters
+ * [0, world) of the local flag array have all reached `target` (the caller keeps the running
+ * total per rank), after which the full output is complete on this rank.  No rank's compute
+ * kernel ever waits for another. */
+typedef struct fg_peers_t {
+  int world;                      /* 1..8 */
+  int rank;
+  long long n_total;              /* = world * N_local, row length of the full output */
+  void* C[8];                     /* full output [M, n_total] fp16 of each rank, as mapped here */
+  unsigned long long* flag[8];    /* flag array (8 x u64, zero at start) of each rank, as mapped here */
+  /* Optional: the activations x are the pushed output of an earlier layer.  The kernel then
+   * reads x only after counters [0, world) at wait_flags (this rank's flag array of that
+   * layer) have reached wait_target; its weight tiles are already on their way by then.
+   * NULL = x is ready when the call is enqueued. */
+  const unsigned long long* wait_flags;
+  unsigned long long wait_target;
+} fg_peers_t;
+
+int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, int K,
+                        const fg_peers_t* peers, void* ws, size_t ws_bytes, fg_stream_t stream);
+int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long long target, void* ws,
+                 fg_stream_t stream);
+
 /* ---- end-to-end convenience (HOST pointers) ---------------------------------
  * x_host and C_host are host buffers (pinned for full speed); W_dev, scales_dev,
  * x_stage_dev (M*K fp16) and C_stage_dev (M*N fp16) are device buffers the caller
