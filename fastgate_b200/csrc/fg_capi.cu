@@ -11,6 +11,7 @@
 
 #include "../../include/fastgate_b200.h"
 #include "fg_kernels.cuh"
+#include "fg_umma.cuh"
 #include "fg_layout.h"
 
 static_assert(FG_TILE_N == fg::kTileN, "layout mismatch");
@@ -18,6 +19,7 @@ static_assert(FG_RED_STRIDE == fg::kRedStride, "layout mismatch");
 static_assert(FG_CHUNK_W_BYTES == fg::kChunkWBytes, "layout mismatch");
 static_assert(FG_MAX_CONSUMER_WARPS == fg::kMaxConsumerWarps, "layout mismatch");
 static_assert(int(FG_ERR_TIMEOUT) == int(fg::kStatusTimeout), "status mismatch");
+static_assert(int(FG_ERR_PLAN) == int(fg::kStatusBadLaunch), "status mismatch");
 static_assert(int(FG_OP_F16_KN) == int(fg::kOpF16KN) && int(FG_OP_F16_NK) == int(fg::kOpF16NK) &&
                   int(FG_OP_W8A16_NK) == int(fg::kOpW8A16NK),
               "op code mismatch");
@@ -55,6 +57,7 @@ struct DeviceInfo {
   int smem_optin = 0;
   int cc_major = 0;
   int smem_set[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
+  int smem_set_umma[3] = {0, 0, 0};
 };
 
 constexpr int kMaxDevices = 64;
@@ -120,6 +123,10 @@ KernelFn pick_kernel(int op, int m_tile) {
   }
 }
 
+KernelFn pick_umma_kernel(int op) {
+  return op == FG_OP_F16_KN ? fg::fg_umma_kernel<fg::kOpF16KN> : fg::fg_umma_kernel<fg::kOpF16NK>;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_common(const void* x, const void* W, const void* C, int M, int N, int K, void* ws,
@@ -132,13 +139,13 @@ int check_common(const void* x, const void* W, const void* C, int M, int N, int 
   return FG_OK;
 }
 
-int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
-                const void* scales, void* C, int M, int N, int K, void* ws, cudaStream_t stream,
-                const fg_peers_t* peers = nullptr) {
-  const int op = pl.op;
-  const int chunks = pl.k_per_stage / fg_chunk_k(op);
-  KernelFn kern = pick_kernel(op, pl.m_tile);
-  int& set = dev->smem_set[op][pl.m_tile == 16];
+// The kernel a plan names, with its shared-memory opt-in done for this device.  Both the
+// workspace entry points and the workspace-free one go through here and through launch_one,
+// so a plan can never be launched with another kernel's thread count or memory layout.
+int prepare_kernel(const fg_plan_t& pl, DeviceInfo* dev, KernelFn* out) {
+  const bool umma = (pl.math == 2);
+  KernelFn kern = umma ? pick_umma_kernel(pl.op) : pick_kernel(pl.op, pl.m_tile);
+  int& set = umma ? dev->smem_set_umma[pl.op] : dev->smem_set[pl.op][pl.m_tile == 16];
   if (pl.smem_bytes > set) {
     const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
@@ -147,6 +154,43 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
       return FG_ERR_CUDA;
     }
     set = pl.smem_bytes;
+  }
+  *out = kern;
+  return FG_OK;
+}
+
+int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const CUtensorMap& tmX,
+               const fg::KParams& p, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.grid);
+  // tcgen05 kernel: fixed warp roles; mma.sync kernel: consumers + one copy-issuing warp +
+  // m_tile/4 warps that finish split tiles
+  cfg.blockDim = dim3(pl.math == 2 ? fg::kUmmaThreads : (pl.consumer_warps + 1 + pl.m_tile / 4) * 32);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = (pl.pdl && p.pdl) ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
+int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
+                const void* scales, void* C, int M, int N, int K, void* ws, cudaStream_t stream,
+                const fg_peers_t* peers = nullptr) {
+  const int op = pl.op;
+  const int chunks = pl.k_per_stage / fg_chunk_k(op);
+  KernelFn kern = nullptr;
+  {
+    const int pst = prepare_kernel(pl, dev, &kern);
+    if (pst != FG_OK) return pst;
   }
 
   CUtensorMap tmW;
@@ -210,23 +254,7 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     if (peers != nullptr)
       for (int q = 0; q < peers->world; ++q)
         p.peer_C[q] = static_cast<__half*>(peers->C[q]) + static_cast<size_t>(m0) * peers->n_total;
-    // consumer warps + one copy-issuing warp + one warp that finishes split tiles
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(pl.grid);
-    cfg.blockDim = dim3((pl.consumer_warps + 2) * 32);
-    cfg.dynamicSmemBytes = pl.smem_bytes;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pl.pdl ? 1 : 0;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
-    if (e != cudaSuccess) {
-      g_last_cuda = static_cast<int>(e);
-      return FG_ERR_CUDA;
-    }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if ((st = launch_one(pl, kern, tmW, tmX, p, stream)) != FG_OK) return st;
   }
   return FG_OK;
 }
@@ -450,17 +478,8 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   pl.pdl = 0;  // a memset precedes every launch, so there is no kernel to overlap with
 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  KernelFn kern = pick_kernel(FG_OP_F16_NK, pl.m_tile);
-  int& set = dev->smem_set[FG_OP_F16_NK][pl.m_tile == 16];
-  if (pl.smem_bytes > set) {
-    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             pl.smem_bytes);
-    if (e != cudaSuccess) {
-      g_last_cuda = static_cast<int>(e);
-      return FG_ERR_CUDA;
-    }
-    set = pl.smem_bytes;
-  }
+  KernelFn kern = nullptr;
+  if ((st = prepare_kernel(pl, dev, &kern)) != FG_OK) return st;
   CUtensorMap tmW;
   if ((st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, W, K, N, 64, 128)) != FG_OK) return st;
 
@@ -499,13 +518,7 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
     if ((st = encode_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xp, K, mp, 64, pl.m_tile)) != FG_OK) return st;
     p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * N;
     p.M = mp;
-    kern<<<pl.grid, (pl.consumer_warps + 2) * 32, pl.smem_bytes, s>>>(tmW, tmX, p);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) {
-      g_last_cuda = static_cast<int>(e);
-      return FG_ERR_CUDA;
-    }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if ((st = launch_one(pl, kern, tmW, tmX, p, s)) != FG_OK) return st;
   }
   return FG_OK;
 }

@@ -43,7 +43,7 @@ constexpr int kMaxPeers = 8;          // ranks of one NVLink box
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then give up
 
 enum { kOpF16KN = 0, kOpF16NK = 1, kOpW8A16NK = 2 };
-enum { kStatusOk = 0, kStatusTimeout = 6 };
+enum { kStatusOk = 0, kStatusTimeout = 6, kStatusBadLaunch = 7 };
 
 template <int OP>
 struct OpTraits;
@@ -278,9 +278,242 @@ __device__ __forceinline__ bool wait_counters(const unsigned long long* flags, i
   return true;
 }
 
-// Warp roles: [0, ncw) consume, ncw produces (TMA), ncw + 1 finishes split tiles.
+// What every role of a CTA needs to know about its share of the work list.
+struct CtaRange {
+  uint32_t KB;     // stages per output tile
+  uint32_t total;  // tiles * KB
+  uint32_t G;      // CTAs
+  uint32_t ub, ue; // this CTA's stages [ub, ue)
+};
+
+// ------------------------------------ producer ------------------------------------------
+// One thread.  Streams this CTA's stages into the ring: per stage the weight tile(s) and the
+// matching slice of the activations, completing on full[s]; a slot is refilled once its
+// consumer has arrived on empty[s].  MT = rows of the activation box.
 template <int OP, int MT>
-__global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
+__device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUtensorMap& tmX, const KParams& p,
+                                             const CtaRange& r, uint32_t smem_base, uint32_t bar_base, int S,
+                                             int cps, unsigned long long* trace) {
+  using T = OpTraits<OP>;
+  constexpr int cbytes = chunk_bytes(OP, MT);
+  const uint32_t stage_bytes = cps * cbytes;
+  const int k_per_stage = cps * T::chunkK;
+  const uint32_t KB = r.KB, ub = r.ub, ue = r.ue;
+  tma_prefetch_desc(&tmW);
+  tma_prefetch_desc(&tmX);
+  const uint64_t pol_w = policy_evict_first();
+  const uint64_t pol_x = policy_evict_last();
+  int tile = static_cast<int>(ub / KB);
+  int kb = static_cast<int>(ub % KB);
+  const int n_it = static_cast<int>(ue - ub);
+  bool dead = false;
+  int issued = 0;
+  if (trace) trace[1] = globaltimer_ns();  // first copy about to be issued
+
+  auto stage_chunks = [&](int kblock) {
+    const int k0 = kblock * k_per_stage;
+    const int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
+    return nch < cps ? nch : cps;
+  };
+  auto issue_w = [&](int s, int tl, int kblock, int nch) {
+    const uint32_t full = bar_base + 8 * s;
+    uint32_t dst = smem_base + s * stage_bytes;
+    for (int c = 0; c < nch; ++c) {
+      const int kc = kblock * k_per_stage + c * T::chunkK;
+      if constexpr (OP == kOpF16KN) {
+        tma_load_2d(dst, &tmW, full, tl * kTileN, kc, pol_w);
+        tma_load_2d(dst + 8192, &tmW, full, tl * kTileN + 64, kc, pol_w);
+      } else {
+        tma_load_2d(dst, &tmW, full, kc, tl * kTileN, pol_w);
+      }
+      dst += cbytes;
+    }
+  };
+  auto issue_x = [&](int s, int kblock, int nch) {
+    const uint32_t full = bar_base + 8 * s;
+    uint32_t dst = smem_base + s * stage_bytes + kChunkWBytes;
+    for (int c = 0; c < nch; ++c) {
+      const int kc = kblock * k_per_stage + c * T::chunkK;
+#pragma unroll
+      for (int xb = 0; xb < T::xBoxes; ++xb)
+        tma_load_2d(dst + xb * MT * 128, &tmX, full, kc + xb * 64, 0, pol_x);
+      dst += cbytes;
+    }
+  };
+
+  // The weight never depends on earlier kernels, so the first ring-full of weight tiles is
+  // requested right away.  Activations may be the output of the previous kernel of the
+  // stream (programmatic dependent launch: this grid may have started while that kernel
+  // was still draining) or of a layer that other ranks are still pushing, so they are
+  // only read after griddepcontrol.wait (a no-op for an ordinary launch) and, if asked,
+  // after the arrival counters of that layer have reached their target.
+  griddep_launch_dependents();
+  const int pre = n_it < S ? n_it : S;
+  {
+    int t2 = tile, k2 = kb;
+    for (int i = 0; i < pre; ++i) {
+      const int nch = stage_chunks(k2);
+      mbar_arrive_expect_tx(bar_base + 8 * i, nch * cbytes);
+      issue_w(i, t2, k2, nch);
+      if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
+    }
+  }
+  griddep_wait();
+  if (p.wait_flags != nullptr && !wait_counters(p.wait_flags, p.wait_world, p.wait_target)) {
+    // The activations never became ready.  Complete the armed stages with what is there
+    // so that no copy is left in flight; the status word tells the caller.
+    atomicExch(p.status, kStatusTimeout);
+  }
+  for (int i = 0; i < pre; ++i) {
+    issue_x(i, kb, stage_chunks(kb));
+    if (++kb == static_cast<int>(KB)) { kb = 0; ++tile; }
+  }
+  int it = pre;
+  issued = pre;
+  for (; it < n_it; ++it) {
+    const int s = it % S;
+    const uint32_t use = it / S;
+    if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
+      dead = true;
+      break;
+    }
+    const int nch = stage_chunks(kb);
+    mbar_arrive_expect_tx(bar_base + 8 * s, nch * cbytes);
+    issue_w(s, tile, kb, nch);
+    issue_x(s, kb, nch);
+    ++issued;
+    if (++kb == static_cast<int>(KB)) {
+      kb = 0;
+      ++tile;
+    }
+  }
+  if (trace) trace[2] = globaltimer_ns();  // last copy issued
+  if (dead) {
+    atomicExch(p.status, kStatusTimeout);
+    // let copies already in flight land before the CTA's shared memory goes away
+    const int back = issued < S ? issued : S;
+    for (int i = issued - back; i < issued; ++i)
+      mbar_wait_bounded(bar_base + 8 * (i % S), (i / S) & 1, kWaitBudgetNs);
+  }
+}
+
+// ------------------------------------ finisher ------------------------------------------
+// MT/4 warps (named barrier kFinBarrier).  They walk the same segment list as the consumers.
+// For every partial segment they wait until all consumer threads have stored their share of
+// the partial tile; one thread publishes it (fence + ticket) and, if this CTA was the last
+// contributor of the tile, the warps add up all partials in CTA order and write C: warp w
+// takes rows 4w..4w+3, lane l columns 4l..4l+3, contributors four at a time, so every lane
+// has sixteen 16-byte loads in flight and the whole tile is fetched in one round trip (two
+// beyond four contributors).  Each element is summed in CTA order whatever the arrival
+// order, which keeps the result bit-reproducible.  The consumers meanwhile go on streaming.
+constexpr int kFinBarrier = 3;
+template <int MT>
+__host__ __device__ constexpr int finisher_warps() { return MT / 4; }
+
+template <int OP, int MT>
+__device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r, uint32_t bar_flush,
+                                             uint32_t bar_fin, volatile uint32_t* prev_slot, int fin_warp,
+                                             int lane, unsigned long long* trace) {
+  constexpr int FW = finisher_warps<MT>();
+  const uint32_t KB = r.KB, total = r.total, G = r.G, ub = r.ub, ue = r.ue;
+  uint32_t u = ub;
+  uint32_t ev = 0;
+  bool dead = false;
+  const bool leader = (fin_warp == 0 && lane == 0);
+  while (u < ue) {
+    const uint32_t tile = u / KB;
+    const uint32_t kb0 = u - tile * KB;
+    const uint32_t len = (KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u);
+    if (len != KB && !dead) {
+      bool ok = mbar_wait_bounded(bar_flush, ev & 1, kWaitBudgetNs * 4);
+      ok = __all_sync(0xffffffffu, ok);
+      const uint32_t c_first = cta_of_unit(tile * KB, total, G);
+      const uint32_t c_last = cta_of_unit(tile * KB + KB - 1, total, G);
+      if (leader) {
+        // a timeout is published like a ticket that is never the last one
+        uint32_t prev = 0xffffffffu;
+        if (ok) {
+          __threadfence();
+          prev = atomicAdd(p.tickets + tile, 1u);
+        } else {
+          atomicExch(p.status, kStatusTimeout);
+        }
+        *prev_slot = prev;
+      }
+      named_bar_sync(kFinBarrier, FW * 32);
+      const uint32_t prev = *prev_slot;
+      if (prev == 0xffffffffu) dead = true;
+      if (prev == c_last - c_first) {
+        __threadfence();
+        const int n0 = tile * kTileN + 4 * lane;
+        const int m0 = 4 * fin_warp;
+        if (m0 < p.M) {
+          float4 sum[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (uint32_t c0 = c_first; c0 <= c_last; c0 += 4) {
+            float4 v[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t c = c0 + j;
+              if (c <= c_last) {
+                const uint32_t cslot = (range_begin(c, total, G) / KB == tile) ? 0u : 1u;
+                const float4* src = reinterpret_cast<const float4*>(
+                    p.partials + (static_cast<size_t>(c) * 2 + cslot) * (MT * kTileN));
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[j][i] = __ldcg(src + (m0 + i) * 32 + lane);
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) v[j][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                sum[i].x += v[j][i].x;
+                sum[i].y += v[j][i].y;
+                sum[i].z += v[j][i].z;
+                sum[i].w += v[j][i].w;
+              }
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int m = m0 + i;
+            if (m < p.M) {
+              store_out2<OP>(p, m, n0, make_float2(sum[i].x, sum[i].y));
+              store_out2<OP>(p, m, n0 + 2, make_float2(sum[i].z, sum[i].w));
+            }
+          }
+        }
+        if (p.world > 0) __threadfence_system();  // this thread's stores into the other ranks' outputs
+      }
+      // every finisher warp has seen this phase of bar_flush and is done with *prev_slot
+      named_bar_sync(kFinBarrier, FW * 32);
+      if (leader) {
+        if (prev == c_last - c_first) {
+          p.tickets[tile] = 0;  // ready for the next launch
+          if (p.world > 0) signal_tile_delivered(p);
+        }
+        mbar_arrive(bar_fin);
+      }
+      ++ev;
+    }
+    u += len;
+  }
+  if (trace && leader) trace[5] = globaltimer_ns();  // finisher done
+}
+
+// Warp roles: [0, ncw) consume, ncw produces (TMA), ncw + 1 ... finish split tiles.
+// The int8 op is planned with at most four consumer warps, which leaves its dequantising
+// inner loop more registers.
+template <int OP, int MT>
+__host__ __device__ constexpr int streamk_max_threads() {
+  return ((OP == kOpW8A16NK ? 4 : kMaxConsumerWarps) + 1 + finisher_warps<MT>()) * 32;
+}
+
+template <int OP, int MT>
+__global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
     fg_streamk_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                       const KParams p) {
   using T = OpTraits<OP>;
@@ -299,6 +532,15 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
   const uint32_t bar_base = smem_base + ring_bytes + red_bytes;  // full[S], empty[S], flush, fin
   const uint32_t bar_flush = bar_base + 16 * S;     // consumers -> finisher: "my partial is stored"
   const uint32_t bar_fin = bar_base + 16 * S + 8;   // finisher -> consumers: "previous partial handled"
+  volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + red_bytes + 16 * S + 16);
+
+  // A launch whose thread count or shared memory does not fit the parameters would index
+  // shared memory out of bounds: refuse it instead (the host reads the status word).
+  if (blockDim.x != static_cast<unsigned>((ncw + 1 + finisher_warps<MT>()) * 32) ||
+      dynamic_smem_size() < 1023u + ring_bytes + red_bytes + 16u * S + 32u) {
+    if (threadIdx.x == 0) atomicExch(p.status, kStatusBadLaunch);
+    return;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -325,198 +567,13 @@ __global__ void __launch_bounds__((kMaxConsumerWarps + 2) * 32, 1)
   const uint32_t ue = range_begin(blockIdx.x + 1, total, G);
   const int k_per_stage = cps * T::chunkK;
 
+  const CtaRange range{KB, total, G, ub, ue};
   if (warp == ncw) {
-    // ------------------------------ producer warp ------------------------------
-    if (lane == 0) {
-      tma_prefetch_desc(&tmW);
-      tma_prefetch_desc(&tmX);
-      const uint64_t pol_w = policy_evict_first();
-      const uint64_t pol_x = policy_evict_last();
-      int tile = static_cast<int>(ub / KB);
-      int kb = static_cast<int>(ub % KB);
-      const int n_it = static_cast<int>(ue - ub);
-      bool dead = false;
-      int issued = 0;
-      if (trace) trace[1] = globaltimer_ns();  // first copy about to be issued
-
-      auto stage_chunks = [&](int kblock) {
-        const int k0 = kblock * k_per_stage;
-        const int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
-        return nch < cps ? nch : cps;
-      };
-      auto issue_w = [&](int s, int tl, int kblock, int nch) {
-        const uint32_t full = bar_base + 8 * s;
-        uint32_t dst = smem_base + s * stage_bytes;
-        for (int c = 0; c < nch; ++c) {
-          const int kc = kblock * k_per_stage + c * T::chunkK;
-          if constexpr (OP == kOpF16KN) {
-            tma_load_2d(dst, &tmW, full, tl * kTileN, kc, pol_w);
-            tma_load_2d(dst + 8192, &tmW, full, tl * kTileN + 64, kc, pol_w);
-          } else {
-            tma_load_2d(dst, &tmW, full, kc, tl * kTileN, pol_w);
-          }
-          dst += cbytes;
-        }
-      };
-      auto issue_x = [&](int s, int kblock, int nch) {
-        const uint32_t full = bar_base + 8 * s;
-        uint32_t dst = smem_base + s * stage_bytes + kChunkWBytes;
-        for (int c = 0; c < nch; ++c) {
-          const int kc = kblock * k_per_stage + c * T::chunkK;
-#pragma unroll
-          for (int xb = 0; xb < T::xBoxes; ++xb)
-            tma_load_2d(dst + xb * MT * 128, &tmX, full, kc + xb * 64, 0, pol_x);
-          dst += cbytes;
-        }
-      };
-
-      // The weight never depends on earlier kernels, so the first ring-full of weight tiles is
-      // requested right away.  Activations may be the output of the previous kernel of the
-      // stream (programmatic dependent launch: this grid may have started while that kernel
-      // was still draining) or of a layer that other ranks are still pushing, so they are
-      // only read after griddepcontrol.wait (a no-op for an ordinary launch) and, if asked,
-      // after the arrival counters of that layer have reached their target.
-      griddep_launch_dependents();
-      const int pre = n_it < S ? n_it : S;
-      {
-        int t2 = tile, k2 = kb;
-        for (int i = 0; i < pre; ++i) {
-          const int nch = stage_chunks(k2);
-          mbar_arrive_expect_tx(bar_base + 8 * i, nch * cbytes);
-          issue_w(i, t2, k2, nch);
-          if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
-        }
-      }
-      griddep_wait();
-      if (p.wait_flags != nullptr && !wait_counters(p.wait_flags, p.wait_world, p.wait_target)) {
-        // The activations never became ready.  Complete the armed stages with what is there
-        // so that no copy is left in flight; the status word tells the caller.
-        atomicExch(p.status, kStatusTimeout);
-      }
-      for (int i = 0; i < pre; ++i) {
-        issue_x(i, kb, stage_chunks(kb));
-        if (++kb == static_cast<int>(KB)) { kb = 0; ++tile; }
-      }
-      int it = pre;
-      issued = pre;
-      for (; it < n_it; ++it) {
-        const int s = it % S;
-        const uint32_t use = it / S;
-        if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
-          dead = true;
-          break;
-        }
-        const int nch = stage_chunks(kb);
-        mbar_arrive_expect_tx(bar_base + 8 * s, nch * cbytes);
-        issue_w(s, tile, kb, nch);
-        issue_x(s, kb, nch);
-        ++issued;
-        if (++kb == static_cast<int>(KB)) {
-          kb = 0;
-          ++tile;
-        }
-      }
-      if (trace) trace[2] = globaltimer_ns();  // last copy issued
-      if (dead) {
-        atomicExch(p.status, kStatusTimeout);
-        // let copies already in flight land before the CTA's shared memory goes away
-        const int back = issued < S ? issued : S;
-        for (int i = issued - back; i < issued; ++i)
-          mbar_wait_bounded(bar_base + 8 * (i % S), (i / S) & 1, kWaitBudgetNs);
-      }
-    }
+    if (lane == 0) run_producer<OP, MT>(tmW, tmX, p, range, smem_base, bar_base, S, cps, trace);
     return;
   }
-
-  if (warp == ncw + 1) {
-    // ------------------------------ finisher warp ------------------------------
-    // Walks the same segment list as the consumers.  For every partial segment it waits
-    // until all consumer threads have stored their share of the partial tile, publishes it
-    // (fence + ticket) and, if this CTA was the last contributor of the tile, adds up all
-    // partials in CTA order and writes C.  The consumers meanwhile go on streaming.
-    uint32_t u = ub;
-    uint32_t ev = 0;
-    bool dead = false;
-    while (u < ue) {
-      const uint32_t tile = u / KB;
-      const uint32_t kb0 = u - tile * KB;
-      const uint32_t len = (KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u);
-      if (len != KB && !dead) {
-        bool ok = mbar_wait_bounded(bar_flush, ev & 1, kWaitBudgetNs * 4);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) {
-          dead = true;
-          if (lane == 0) atomicExch(p.status, kStatusTimeout);
-        } else {
-          const uint32_t c_first = cta_of_unit(tile * KB, total, G);
-          const uint32_t c_last = cta_of_unit(tile * KB + KB - 1, total, G);
-          const uint32_t n_contrib = c_last - c_first + 1;
-          unsigned int prev = 0;
-          if (lane == 0) {
-            __threadfence();
-            prev = atomicAdd(p.tickets + tile, 1u);
-          }
-          prev = __shfl_sync(0xffffffffu, prev, 0);
-          if (prev == n_contrib - 1) {
-            __threadfence();
-            // Lane l owns columns 4l..4l+3 of every row.  Rows go four at a time and
-            // contributors four at a time, so sixteen 16-byte loads are in flight; each
-            // element is still summed in CTA order, which keeps the result deterministic.
-            const int n0 = tile * kTileN + 4 * lane;
-            for (int m0 = 0; m0 < MT && m0 < p.M; m0 += 4) {
-              float4 sum[4];
-#pragma unroll
-              for (int i = 0; i < 4; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (uint32_t c0 = c_first; c0 <= c_last; c0 += 4) {
-                float4 v[4][4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint32_t c = c0 + j;
-                  if (c <= c_last) {
-                    const uint32_t cslot = (range_begin(c, total, G) / KB == tile) ? 0u : 1u;
-                    const float4* src = reinterpret_cast<const float4*>(
-                        p.partials + (static_cast<size_t>(c) * 2 + cslot) * (MT * kTileN));
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) v[j][i] = __ldcg(src + (m0 + i) * 32 + lane);
-                  } else {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) v[j][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                  }
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j)
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    sum[i].x += v[j][i].x;
-                    sum[i].y += v[j][i].y;
-                    sum[i].z += v[j][i].z;
-                    sum[i].w += v[j][i].w;
-                  }
-              }
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int m = m0 + i;
-                if (m < p.M) {
-                  store_out2<OP>(p, m, n0, make_float2(sum[i].x, sum[i].y));
-                  store_out2<OP>(p, m, n0 + 2, make_float2(sum[i].z, sum[i].w));
-                }
-              }
-            }
-            if (lane == 0) p.tickets[tile] = 0;  // ready for the next launch
-            if (p.world > 0) {
-              __threadfence_system();
-              __syncwarp();
-              if (lane == 0) signal_tile_delivered(p);
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_fin);
-        ++ev;
-      }
-      u += len;
-    }
-    if (trace && lane == 0) trace[5] = globaltimer_ns();  // finisher done
+  if (warp > ncw) {
+    run_finisher<OP, MT>(p, range, bar_flush, bar_fin, prev_slot, warp - ncw - 1, lane, trace);
     return;
   }
 

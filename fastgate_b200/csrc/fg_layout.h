@@ -24,10 +24,16 @@ static inline int fg_x_boxes(int op) { return op == 2 ? 2 : 1; }
 static inline int fg_chunk_bytes(int op, int m_tile) {
   return FG_CHUNK_W_BYTES + fg_x_boxes(op) * m_tile * 128;
 }
-/* reduction buffer + 1 KB alignment slack + flag word (the barriers are counted per stage) */
+/* reduction buffer + 1 KB alignment slack + two hand-off barriers and the finishers' ticket
+ * word (the ring's barriers are counted per stage) */
 static inline int fg_fixed_smem_bytes(int consumer_warps, int m_tile) {
-  return 1024 + consumer_warps * m_tile * FG_RED_STRIDE * 4 + 16;
+  return 1024 + consumer_warps * m_tile * FG_RED_STRIDE * 4 + 32;
 }
 static inline int fg_smem_bytes(int op, int m_tile, int chunks, int stages, int consumer_warps) {
   return fg_fixed_smem_bytes(consumer_warps, m_tile) + stages * (chunks * fg_chunk_bytes(op, m_tile) + 16);
+}
+
+/* tcgen05 variant: ring + barriers only (the accumulators live in tensor memory) */
+static inline int fg_umma_smem_bytes(int op, int chunks, int stages) {
+  return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + 64;
 }

@@ -31,6 +31,32 @@ extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin
   p.tiles = N / 128;
 
   const int chunk_k = fg_chunk_k(op);
+  if (op != FG_OP_W8A16_NK && p.m_tile == 16) {
+    // fp16 weights, more than 8 token rows: the tcgen05 kernel (accumulator in tensor memory,
+    // no cross-warp reduction, the whole shared memory is ring).  Its single MMA-issuing
+    // thread pays a fixed cost per stage, so stages are as large as the work allows:
+    // measured on B200, 64 KB stages beat 32 KB beat 16 KB as long as a CTA still gets
+    // enough of them to balance the load.
+    p.math = 2;
+    p.consumer_warps = 4;  // epilogue warps, fixed
+    int chunks = 4;
+    for (; chunks > 1; chunks >>= 1) {
+      const long long kb = (K + chunks * chunk_k - 1) / (chunks * chunk_k);
+      if (static_cast<long long>(p.tiles) * kb >= 6LL * sm_count) break;
+    }
+    p.k_per_stage = chunks * chunk_k;
+    p.k_blocks = (K + p.k_per_stage - 1) / p.k_per_stage;
+    const long long units = static_cast<long long>(p.tiles) * p.k_blocks;
+    p.grid = static_cast<int>(std::min<long long>(std::min(sm_count, FG_MAX_GRID), units));
+    if (units * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;
+    const int stage_bytes = chunks * fg_chunk_bytes(op, 16);
+    p.stages = std::min((smem_optin_bytes - 1024 - 64) / (stage_bytes + 16), FG_MAX_STAGES);
+    if (p.stages < 2) return FG_ERR_PLAN;
+    p.pdl = 1;
+    p.smem_bytes = fg_umma_smem_bytes(op, chunks, p.stages);
+    *out = p;
+    return FG_OK;
+  }
   // One 16 KB weight chunk per stage: measured on B200, deeper rings of small stages beat
   // fewer large ones for every shape tried (the ring is what a dependent launch prefetches
   // while its predecessor drains).
@@ -70,21 +96,29 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (smem_optin_bytes <= 0) smem_optin_bytes = 232448;
   if (p->op < FG_OP_F16_KN || p->op > FG_OP_W8A16_NK) return FG_ERR_PLAN;
   if (p->m_tile != 8 && p->m_tile != 16) return FG_ERR_PLAN;
+  if (p->math != 0 && p->math != 2) return FG_ERR_PLAN;
   const int chunk_k = fg_chunk_k(p->op);
   if (p->k_per_stage <= 0 || p->k_per_stage % chunk_k) return FG_ERR_PLAN;
   const int chunks = p->k_per_stage / chunk_k;
   if (chunks < 1 || chunks > 4) return FG_ERR_PLAN;
-  if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
   if (p->stages < 2 || p->stages > FG_MAX_STAGES) return FG_ERR_PLAN;
-  // each stage must always meet the same consumer warp (see fg_plan)
-  if (p->stages % p->consumer_warps) return FG_ERR_PLAN;
+  if (p->math == 2) {
+    // tcgen05 variant: fp16 weights, 16-row accumulator in tensor memory, fixed warp roles
+    if (p->op == FG_OP_W8A16_NK || p->m_tile != 16) return FG_ERR_PLAN;
+  } else {
+    if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
+    if (p->op == FG_OP_W8A16_NK && p->consumer_warps > 4) return FG_ERR_PLAN;  // the int8 kernel is built for <= 4
+    // each stage must always meet the same consumer warp (see fg_plan)
+    if (p->stages % p->consumer_warps) return FG_ERR_PLAN;
+  }
   if (p->tiles != N / 128) return FG_ERR_PLAN;
   if (p->k_blocks != (K + p->k_per_stage - 1) / p->k_per_stage) return FG_ERR_PLAN;
   const long long units = static_cast<long long>(p->tiles) * p->k_blocks;
   if (p->grid < 1 || p->grid > FG_MAX_GRID || p->grid > units) return FG_ERR_PLAN;
   if (units * p->grid >= (1LL << 31)) return FG_ERR_PLAN;  // the kernel's index math is 32-bit
-  if (p->smem_bytes != fg_smem_bytes(p->op, p->m_tile, chunks, p->stages, p->consumer_warps))
-    return FG_ERR_PLAN;
+  const int want_smem = (p->math == 2) ? fg_umma_smem_bytes(p->op, chunks, p->stages)
+                                       : fg_smem_bytes(p->op, p->m_tile, chunks, p->stages, p->consumer_warps);
+  if (p->smem_bytes != want_smem) return FG_ERR_PLAN;
   if (p->smem_bytes > smem_optin_bytes) return FG_ERR_PLAN;
   return FG_OK;
 }

@@ -75,7 +75,8 @@ typedef struct fg_plan_t {
   int k_blocks;      /* ceil(K / k_per_stage): stages per output tile          */
   int smem_bytes;    /* dynamic shared memory per CTA                          */
   int passes;        /* ceil(M / 16) launches                                  */
-  int math;          /* 0 = mma.sync tensor-core tiles, 1 = CUDA-core FMA (reserved) */
+  int math;          /* 0 = mma.sync tiles, accumulators in registers; 2 = tcgen05.mma, accumulator
+                        in tensor memory (fp16 weights, m_tile 16); 1 reserved                */
   int pdl;           /* 1 = programmatic dependent launch: the kernel may start, and prefetch
                         weight tiles, while the previous kernel of the stream drains; it reads
                         activations and writes nothing before that kernel has completed       */
@@ -97,8 +98,9 @@ int fg_plan_validate(const fg_plan_t* plan, int N, int K, int smem_optin_bytes);
  * that may overlap on the GPU need separate workspaces. */
 size_t fg_workspace_bytes(int N);
 int fg_workspace_init(void* ws, size_t ws_bytes, fg_stream_t stream);
-/* Synchronises `stream`, copies the device status word to *status_out (FG_OK or
- * FG_ERR_TIMEOUT) and clears it. */
+/* Synchronises `stream`, copies the device status word to *status_out (FG_OK,
+ * FG_ERR_TIMEOUT, or FG_ERR_PLAN if a kernel refused a launch that did not fit its
+ * parameters) and clears it. */
 int fg_workspace_status(void* ws, int* status_out, fg_stream_t stream);
 
 /* ---- compute entry points (device pointers) --------------------------------

@@ -206,7 +206,8 @@ def test_linearity_and_row_independence(dev, ws):
 
 
 def test_layouts_agree_bitwise(dev, ws):
-    """KxN and NxK storage of the same weight give the same bits (same summation order)."""
+    """KxN and NxK storage of the same weight give the same bits (same summation order),
+    in the tcgen05 kernel (16 rows) and in the mma.sync kernel (8 rows)."""
     case = wl.Case("kn_vs_nk", wl.OP_NK, 16, 4096, 4096, 99)
     x, W, _ = inputs(case)
     a = torch.zeros(16, 4096, dtype=torch.float16, device=dev)
@@ -214,6 +215,11 @@ def test_layouts_agree_bitwise(dev, ws):
     assert gu.call(wl.OP_NK, x.to(dev), W.to(dev), None, a, 16, 4096, 4096, ws) == capi.FG_OK
     assert gu.call(wl.OP_KN, x.to(dev), W.t().contiguous().to(dev), None, b, 16, 4096, 4096, ws) == capi.FG_OK
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    a8 = torch.zeros(8, 4096, dtype=torch.float16, device=dev)
+    b8 = torch.zeros(8, 4096, dtype=torch.float16, device=dev)
+    assert gu.call(wl.OP_NK, x[:8].contiguous().to(dev), W.to(dev), None, a8, 8, 4096, 4096, ws) == capi.FG_OK
+    assert gu.call(wl.OP_KN, x[:8].contiguous().to(dev), W.t().contiguous().to(dev), None, b8, 8, 4096, 4096, ws) == capi.FG_OK
+    assert torch.equal(a8.view(torch.int16), b8.view(torch.int16))
 
 
 def test_n_shards_concatenate_to_the_full_result(dev, ws):
@@ -243,12 +249,13 @@ def _edited(base, N, K, op, m_tile, chunks, warps, stages, grid, pdl):
     ctypes.memmove(ctypes.byref(p), ctypes.byref(base), ctypes.sizeof(p))
     ck = 128 if op == wl.OP_W8 else 64
     p.m_tile = m_tile
+    p.math = 0
     p.k_per_stage = chunks * ck
     p.k_blocks = -(-K // p.k_per_stage)
     p.consumer_warps, p.stages, p.pdl = warps, stages, pdl
     p.grid = min(grid, p.tiles * p.k_blocks)
     cb = chunks * (16384 + (2 if op == wl.OP_W8 else 1) * m_tile * 128)
-    p.smem_bytes = 1024 + warps * m_tile * 132 * 4 + 16 + stages * (cb + 16)
+    p.smem_bytes = 1024 + warps * m_tile * 132 * 4 + 32 + stages * (cb + 16)
     return p if capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK else None
 
 
@@ -271,6 +278,46 @@ def test_plan_walk(op, dev, ws):
                 run_case(case, dev, ws, plan=p, check_twice=False)
                 tried += 1
     assert tried >= 30
+
+
+def _edited_umma(base, N, K, op, chunks, stages, grid, pdl):
+    p = capi.Plan()
+    ctypes.memmove(ctypes.byref(p), ctypes.byref(base), ctypes.sizeof(p))
+    p.m_tile, p.math, p.consumer_warps, p.pdl = 16, 2, 4, pdl
+    p.k_per_stage = chunks * 64
+    p.k_blocks = -(-K // p.k_per_stage)
+    p.stages = stages
+    p.grid = min(grid, p.tiles * p.k_blocks)
+    p.smem_bytes = 1024 + stages * (chunks * 18432 + 16) + 64
+    return p if capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK else None
+
+
+@pytest.mark.parametrize("op", [wl.OP_KN, wl.OP_NK])
+def test_plan_walk_tcgen05(op, dev, ws):
+    """The tcgen05 kernel over ring depths, stage sizes, grid sizes, with and without PDL,
+    for every M (it serves any M <= 16 per pass; the planner only picks it above 8)."""
+    N, K = 1152, 2304
+    tried = 0
+    for M in (1, 5, 8, 11, 16, 21):
+        case = wl.Case(f"umma_walk_op{op}_M{M}", op, M, N, K, 61 + M)
+        base = capi.plan(op, M, N, K, 148, 232448)
+        for chunks, stages, grid, pdl in [(1, 2, 148, 0), (1, 12, 148, 1), (2, 6, 148, 1), (4, 3, 148, 0), (3, 4, 17, 1),
+                                          (1, 5, 1, 0), (2, 2, 148, 1), (1, 7, 97, 0)]:
+            p = _edited_umma(base, N, K, op, chunks, stages, grid, pdl)
+            assert p is not None
+            run_case(case, dev, ws, plan=p, check_twice=(tried % 5 == 0))
+            tried += 1
+    assert tried == 48
+
+
+def test_ragged_last_stage_tcgen05(dev, ws):
+    for (op, K) in [(wl.OP_NK, 384), (wl.OP_KN, 640), (wl.OP_NK, 896)]:
+        N, M = 256, 13
+        base = capi.plan(op, M, N, K, 148, 232448)
+        for chunks in (2, 4):
+            p = _edited_umma(base, N, K, op, chunks, 3, 148, 1)
+            assert p is not None
+            run_case(wl.Case(f"umma_ragged_op{op}_K{K}_c{chunks}", op, M, N, K, K + chunks), dev, ws, plan=p)
 
 
 def test_ragged_last_stage(dev, ws):

@@ -71,7 +71,14 @@ def test_plan_invariants(op, M, N, K):
     assert p.k_per_stage % CHUNK_K[op] == 0
     assert p.k_blocks == -(-K // p.k_per_stage)
     assert 1 <= p.grid <= min(148, p.tiles * p.k_blocks)
-    assert p.stages >= 2 and p.stages % p.consumer_warps == 0, "a ring slot must always meet the same warp"
+    assert p.stages >= 2
+    if p.math == 0:
+        assert p.stages % p.consumer_warps == 0, "a ring slot must always meet the same warp"
+        if op == 2:
+            assert p.consumer_warps <= 4
+    else:
+        assert p.math == 2 and op != 2 and p.m_tile == 16, "tcgen05 kernel: fp16 weights, 16-row accumulator"
+    assert (p.math == 2) == (op != 2 and M > 8), "more than 8 rows of fp16 go to the tcgen05 kernel"
     assert p.smem_bytes <= 232448
     assert p.passes == -(-M // 16)
     assert capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK
@@ -97,7 +104,8 @@ def test_plan_rejects_bad_problems():
 
 def test_validate_catches_edited_plans():
     L = capi.lib
-    good = capi.plan(1, 16, 8192, 8192, **B200)
+    good = capi.plan(1, 8, 8192, 8192, **B200)
+    assert good.math == 0
 
     def edited(**kw):
         q = capi.Plan()
@@ -116,6 +124,24 @@ def test_validate_catches_edited_plans():
     assert edited(tiles=good.tiles + 1) == capi.FG_ERR_PLAN
     assert edited(k_per_stage=96) == capi.FG_ERR_PLAN
     assert edited(smem_bytes=good.smem_bytes + 16) == capi.FG_ERR_PLAN
+    assert edited(math=1) == capi.FG_ERR_PLAN
+    assert edited(math=2) == capi.FG_ERR_PLAN           # the tcgen05 kernel needs the 16-row tile
+
+    umma = capi.plan(1, 16, 8192, 8192, **B200)
+    assert umma.math == 2
+
+    def edited2(**kw):
+        q = capi.Plan()
+        ctypes.memmove(ctypes.byref(q), ctypes.byref(umma), ctypes.sizeof(q))
+        for k, v in kw.items():
+            setattr(q, k, v)
+        return L.fg_plan_validate(ctypes.byref(q), 8192, 8192, 232448)
+
+    assert edited2() == capi.FG_OK
+    assert edited2(stages=umma.stages + 1) == capi.FG_ERR_PLAN
+    assert edited2(m_tile=8) == capi.FG_ERR_PLAN
+    assert edited2(op=2) == capi.FG_ERR_PLAN
+    assert edited2(math=0) == capi.FG_ERR_PLAN          # another kernel, another shared-memory layout
 
 
 def test_default_device_is_b200():
