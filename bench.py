@@ -50,7 +50,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--workload", choices=("bt_sweep",), default="bt_sweep")
+    ap.add_argument("--workload", choices=("bt_sweep", "cfg1", "cfg3", "cfg4", "dit"), default="bt_sweep",
+                    help="bt_sweep (default, config 2) | cfg1 edgemm_m8n128k64x4 | cfg3 fastgemv | cfg4 fastgemv_int8 | "
+                         "dit: the 40-layer DiT linear stack, N-sharded over the GPUs (strong scaling)")
+    ap.add_argument("--layers", type=int, default=40, help="dit: number of layers")
     ap.add_argument("--no-graph", action="store_true", help="launch on a stream instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -374,6 +377,167 @@ def run_ours(args):
     return line
 
 
+def _graph_time(step_fn, steps, warmup, world, stream, use_graph):
+    import torch
+
+    graph = None
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            step_fn()
+        torch.cuda.synchronize()
+        if use_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step_fn()
+    return time_steps(step_fn, steps, warmup, world, stream, graph=graph), graph is not None
+
+
+def run_other_workload(args):
+    """Configs 1, 3, 4 (single GPU) and 5 (the DiT stack, N-sharded over the ranks)."""
+    import torch
+
+    import fastgate_b200 as fg
+    from fastgate_b200 import shard, workloads as wl
+
+    world, rank, local = dist_setup(args)
+    dev = torch.device("cuda", local)
+    stream = torch.cuda.Stream(device=dev)
+    peak, peak_kind = measured_peak()
+    name = args.workload
+    extra = {}
+    if name != "dit":
+        if world != 1:
+            raise SystemExit(f"--workload {name} is a single-GPU workload")
+        cases = {"cfg1": wl.cfg1, "cfg3": wl.cfg3, "cfg4": wl.cfg4}[name]()
+        copies = []  # per case: rotating weight copies beyond the L2 size
+        for c in cases:
+            n_rot = max(2, -(-600 * 2 ** 20 // c.weight_bytes))
+            w0 = wl.make_weight(c).to(dev)
+            copies.append([w0] + [w0.clone() for _ in range(n_rot - 1)])
+        xs = [wl.make_activation(c).to(dev) for c in cases]
+        scs = [wl.make_scales(c) for c in cases]
+        scs = [t.to(dev) if t is not None else None for t in scs]
+        outs = [torch.zeros(c.M, c.N, dtype=torch.float16, device=dev) for c in cases]
+        state = {"i": 0}
+
+        def call(ci, w):
+            c = cases[ci]
+            if c.op == wl.OP_KN:
+                fg.edgemm_m8n128k64x4(xs[ci], w, outs[ci])
+            elif c.op == wl.OP_NK:
+                fg.fastgemv(w, xs[ci], outs[ci])
+            else:
+                fg.fastgemv_int8(w, xs[ci], outs[ci], scs[ci])
+
+        n_rot_all = max(len(c) for c in copies)
+
+        def step_once():
+            for ci in range(len(cases)):
+                call(ci, copies[ci][state["i"] % len(copies[ci])])
+            state["i"] += 1
+
+        def step():  # one graph = every rotation, so that a replay never re-reads a cached weight
+            for _ in range(n_rot_all):
+                step_once()
+
+        n0 = fg.launch_count()
+        sampler = ClockSampler(local)
+        reps = max(1, -(-args.steps // n_rot_all))
+        ms, graphed = _graph_time(step, reps, max(1, -(-args.warmup // n_rot_all)), 1, stream, not args.no_graph)
+        clocks = sampler.stop()
+        steps_done = reps * n_rot_all
+        ms_step = ms / steps_done
+        bytes_step = sum(c.algorithmic_bytes for c in cases)
+        launches = steps_done * len(cases)
+        workload = {"cfg1": "edgemm_m8n128k64x4: M=8, K=N=4096, weight KxN fp16",
+                    "cfg3": "fastgemv: M=1, weight 11008x4096 and 4096x11008 fp16 (NxK)",
+                    "cfg4": "fastgemv_int8: M in {1,8}, weight int8 28672x8192 + fp16 scale per output channel"}[name]
+        sharding = "single GPU"
+        scaling = "weak"
+        metric = "effective HBM GB/s of M<=16 fp16/int8 GEMM-GEMV"
+        n_calls = len(cases)
+    else:
+        cases_all = wl.cfg5(args.layers)
+        g = torch.Generator(device=dev).manual_seed(5000 + rank)
+        layers, xs = [], []
+        for c in cases_all:  # this rank's rows of every weight (seeded on the device: 9 GB in total)
+            n_loc = c.N // world
+            w = (torch.randn(n_loc, c.K, device=dev, generator=g, dtype=torch.float32) / c.K ** 0.5).to(torch.float16)
+            layers.append(shard.ShardedLinear(w, c.N))
+        for j in range(4):
+            xs.append(torch.randn(16, wl.DIT_LINEARS[j][2], device=dev, generator=g).to(torch.float16))
+        state = {"i": 0}
+
+        def step_local():
+            for i, lay in enumerate(layers):
+                lay.forward_local(xs[i % 4])
+
+        def step_nccl():
+            for i, lay in enumerate(layers):
+                lay.forward(xs[i % 4])
+
+        def step_push():
+            prev = None
+            for i, lay in enumerate(layers):
+                lay.forward_push(xs[i % 4], wait=False, after=prev)
+                prev = lay.last_push(16)
+            lay.push_wait(prev)
+
+        n0 = fg.launch_count()
+        sampler = ClockSampler(local) if rank == 0 else None
+        ms_local, graphed = _graph_time(step_local, args.steps, args.warmup, world, stream, (not args.no_graph) and world == 1)
+        ms, gather_kind = ms_local, "none (single GPU)"
+        if world > 1:
+            ms_nccl, _ = _graph_time(step_nccl, args.steps, args.warmup, world, stream, False)
+            ms, gather_kind = ms_nccl, "NCCL all_gather_into_tensor + copy per linear"
+            extra["nccl_gather"] = {"ms_per_step": ms_nccl / args.steps}
+            if not args.no_push:
+                try:
+                    ms_push, _ = _graph_time(step_push, args.steps, args.warmup, world, stream, False)
+                    ms, gather_kind = ms_push, "fused: tiles pushed into every rank's output + in-kernel dependency wait"
+                except Exception as e:
+                    sys.stderr.write(f"rank {rank}: fused all-gather unavailable ({e})\n")
+        clocks = sampler.stop() if sampler else None
+        steps_done = args.steps
+        ms_step = ms / steps_done
+        bytes_step = sum(c.algorithmic_bytes for c in cases_all)  # whole model, whatever the number of ranks
+        extra["no_gather"] = {"value": bytes_step / (ms_local / steps_done) / 1e6, "unit": "GB/s",
+                              "ms_per_step": ms_local / steps_done}
+        if "nccl_gather" in extra:
+            extra["nccl_gather"]["value"] = bytes_step / extra["nccl_gather"]["ms_per_step"] / 1e6
+            extra["nccl_gather"]["unit"] = "GB/s"
+        launches = steps_done * len(cases_all)
+        workload = (f"dit: {args.layers} layers x (3072->9216, 3072->3072, 3072->12288, 12288->3072), M=16, fp16, "
+                    f"weights NxK, {sum(c.weight_bytes for c in cases_all) / 1e9:.2f} GB")
+        sharding = f"N-sharded over {world} GPUs; gather: {gather_kind}" if world > 1 else "single GPU"
+        scaling = "strong"
+        metric = "effective HBM GB/s of the DiT linear stack (M=16 fp16 GEMM, N-sharded)"
+        n_calls = len(cases_all)
+        ms_step_local = ms_local / steps_done
+    if rank != 0:
+        return None
+    if name != "dit":
+        ms_step_local = ms_step
+    per_rank_bytes = bytes_step / (world if name == "dit" else 1)
+    achieved = per_rank_bytes / n_calls / (ms_step_local / 1e3 / n_calls) / 1e9
+    line = {
+        "metric": metric, "value": bytes_step / ms_step / 1e6, "unit": "GB/s", "n_gpus": world, "steps": steps_done,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+        "dtype": "int8 weights, f16 activations (fp32 accumulate)" if name == "cfg4" else "f16 (fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": workload, "calls_per_step": n_calls, "sharding": sharding,
+                   "l2": "weights rotate over more than 600 MB" if name != "dit" else "9 GB of distinct weights per pass",
+                   "launch": "cuda graph replay" if graphed else "stream launches"},
+        "us_per_call": ms_step * 1e3 / n_calls,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0, "traffic": None,
+                     "kernel": "fg::fg_streamk_kernel / fg::fg_umma_kernel"},
+        "clocks": clocks, "gpu_launches": int(launches), "e2e": None,
+    }
+    line.update(extra)
+    return line
+
+
 def run_reference(args):
     """The reference's own implementation of the path: its kernels rebuilt for sm_100a when
     available (and a GPU is present), else the CPU oracle port on the host cores."""
@@ -469,7 +633,12 @@ def run_reference(args):
 
 def main():
     args = parse_args()
-    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if args.impl == "reference":
+        line = run_reference(args)
+    elif args.workload == "bt_sweep":
+        line = run_ours(args)
+    else:
+        line = run_other_workload(args)
     try:
         import torch.distributed as dist
         if dist.is_initialized():

@@ -442,7 +442,7 @@ int fg_trace_read(void* ws, unsigned long long* out, int ctas, fg_stream_t strea
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   uint8_t* src = static_cast<uint8_t*>(ws) + FG_WS_HEADER_BYTES +
                  static_cast<size_t>(kTraceFirstCta) * 2 * FG_WS_PARTIAL_TILE_BYTES;
-  const size_t bytes = static_cast<size_t>(ctas) * 8 * sizeof(unsigned long long);
+  const size_t bytes = static_cast<size_t>(ctas) * fg::kTraceSlots * sizeof(unsigned long long);
   cudaError_t e = cudaMemcpyAsync(out, src, bytes, cudaMemcpyDeviceToHost, s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
   if (e == cudaSuccess) e = cudaMemsetAsync(src, 0, bytes, s);

@@ -40,6 +40,7 @@ constexpr int kRedStride = 132;       // floats per row of the cross-warp reduct
 constexpr int kChunkWBytes = 16384;   // weight bytes per chunk (128 columns x 128 B, or 64 k x 256 B)
 constexpr int kMaxConsumerWarps = 8;
 constexpr int kMaxPeers = 8;          // ranks of one NVLink box
+constexpr int kTraceSlots = 16;       // 64-bit words per CTA of the built-in tracer
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then give up
 
 enum { kOpF16KN = 0, kOpF16NK = 1, kOpW8A16NK = 2 };
@@ -69,7 +70,7 @@ struct KParams {
   float* partials;           // [grid][2][MT * 128]
   unsigned int* tickets;     // [tiles], zero between launches
   int* status;               // device status word
-  unsigned long long* trace; // nullptr, or 8 timestamps (ns) per CTA for the built-in tracer
+  unsigned long long* trace; // nullptr, or kTraceSlots words per CTA for the built-in tracer
   int M, N, K;
   int tiles;                 // N / 128
   int k_blocks;              // stages per tile
@@ -373,10 +374,12 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
   for (; it < n_it; ++it) {
     const int s = it % S;
     const uint32_t use = it / S;
+    const unsigned long long tw0 = trace ? globaltimer_ns() : 0;
     if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
       dead = true;
       break;
     }
+    if (trace) trace[8] += globaltimer_ns() - tw0;  // waiting for a free slot
     const int nch = stage_chunks(kb);
     mbar_arrive_expect_tx(bar_base + 8 * s, nch * cbytes);
     issue_w(s, tile, kb, nch);
@@ -545,7 +548,7 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int nct = ncw * 32;
-  unsigned long long* trace = p.trace ? p.trace + 8 * blockIdx.x : nullptr;
+  unsigned long long* trace = p.trace ? p.trace + kTraceSlots * blockIdx.x : nullptr;
   if (trace && threadIdx.x == 0) trace[0] = globaltimer_ns();  // CTA start
 
   if (threadIdx.x == 0) {

@@ -73,7 +73,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 // Shared-memory matrix descriptor, 128B swizzle (layout type 2), descriptor version 1.
 // Addresses and offsets in units of 16 bytes.
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo16, uint32_t sbo16) {
+__host__ __device__ constexpr uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo16, uint32_t sbo16) {
   return static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>(lbo16 & 0x3FFFu) << 16) |
          (static_cast<uint64_t>(sbo16 & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
 }
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  unsigned long long* trace = p.trace ? p.trace + 8 * blockIdx.x : nullptr;
+  unsigned long long* trace = p.trace ? p.trace + kTraceSlots * blockIdx.x : nullptr;
   if (trace && threadIdx.x == 0) trace[0] = globaltimer_ns();
 
   if (threadIdx.x == 0) {
@@ -197,30 +197,41 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT);
         for (int it = it0; it < it0 + len; ++it) {
           const int s = it % S;
+          const unsigned long long tw0 = trace ? globaltimer_ns() : 0;
           if (!mbar_wait_bounded(bar_base + 8 * s, (it / S) & 1, kWaitBudgetNs)) {
             dead = true;
             break;
           }
-          if (trace && it == 0) trace[3] = globaltimer_ns();  // first stage landed
+          const unsigned long long tw1 = trace ? globaltimer_ns() : 0;
+          if (trace) trace[9] += tw1 - tw0;                   // waiting for the stage to land
+          if (trace && it == 0) trace[3] = tw1;               // first stage landed
           const int k0 = (kb0 + (it - it0)) * k_per_stage;
           int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
           nch = nch < cps ? nch : cps;
+          // Descriptors differ only in their start-address field (bits 0-13, in 16-byte units;
+          // shared-memory addresses stay below 2^18), so a chunk's descriptor is one OR and
+          // each k16 step one add: this thread is alone in issuing and its instruction
+          // latency, not the tensor core, bounds the rate.
+          // K-major: a k16 step is 32 bytes further along the 128-byte rows (8-row groups
+          // 1024 B apart).  MN-major: it is sixteen 128-byte k-rows = 2048 B further; the
+          // two 64-column boxes are 8192 B apart (LBO), 8-row k-groups 1024 B (SBO).
+          constexpr uint64_t a_hi = (OP == kOpF16NK) ? umma_smem_desc(0, 1, 64) : umma_smem_desc(0, 512, 64);
+          constexpr uint64_t b_hi = umma_smem_desc(0, 1, 64);
+          constexpr uint64_t a_step = (OP == kOpF16NK) ? 2 : 128;
           uint32_t wb = smem_base + s * stage_bytes;
+          uint32_t acc_flag = (it > it0) ? 1u : 0u;
           for (int c = 0; c < nch; ++c) {
-            const uint32_t xb = wb + kChunkWBytes;
-#pragma unroll
-            for (int kk = 0; kk < 4; ++kk) {
-              // K-major: a k16 step is 32 bytes further along the 128-byte rows (8-row groups
-              // 1024 B apart).  MN-major: it is sixteen 128-byte k-rows = 2048 B further; the
-              // two 64-column boxes are 8192 B apart (LBO), 8-row k-groups 1024 B (SBO).
-              const uint64_t adesc = (OP == kOpF16NK) ? umma_smem_desc(wb + kk * 32, 1, 64)
-                                                      : umma_smem_desc(wb + kk * 2048, 512, 64);
-              const uint64_t bdesc = umma_smem_desc(xb + kk * 32, 1, 64);
-              umma_f16(tmem_d + (kk & 1) * kUmmaMT, adesc, bdesc, idesc, (it > it0 || c > 0 || kk > 1) ? 1u : 0u);
-            }
+            const uint64_t a0 = a_hi | (wb >> 4);
+            const uint64_t b0 = b_hi | ((wb + kChunkWBytes) >> 4);
+            umma_f16(tmem_d, a0, b0, idesc, acc_flag);
+            umma_f16(tmem_d + kUmmaMT, a0 + a_step, b0 + 2, idesc, acc_flag);
+            umma_f16(tmem_d, a0 + 2 * a_step, b0 + 4, idesc, 1u);
+            umma_f16(tmem_d + kUmmaMT, a0 + 3 * a_step, b0 + 6, idesc, 1u);
+            acc_flag = 1u;
             wb += cbytes;
           }
           umma_commit(bar_base + 8 * (S + s));  // the slot is free once these MMAs have read it
+          if (trace) trace[10] += globaltimer_ns() - tw1;     // issuing
         }
         if (dead) break;
         umma_commit(bar_acc_full + 8 * b);
@@ -247,6 +258,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       uint32_t r[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) r[i] = 0;
+      const unsigned long long te0 = (trace && threadIdx.x == 0) ? globaltimer_ns() : 0;
       if (!dead) {
         bool ok = mbar_wait_bounded(bar_acc_full + 8 * b, use & 1, kWaitBudgetNs * 2);
         ok = __all_sync(0xffffffffu, ok);
@@ -265,7 +277,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);  // the MMA warp may reuse this accumulator
       }
-      if (trace && threadIdx.x == 0) trace[7] = globaltimer_ns();  // accumulator read back
+      if (trace && threadIdx.x == 0) {
+        trace[7] = globaltimer_ns();  // accumulator read back
+        trace[11] += trace[7] - te0;  // waiting for it
+      }
       const int n = tile * kTileN + n_in_tile;
       if (whole) {
         float sc = 1.f;

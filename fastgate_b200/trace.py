@@ -20,7 +20,8 @@ from . import capi
 OPS = {"kn": capi.FG_OP_F16_KN, "nk": capi.FG_OP_F16_NK, "w8": capi.FG_OP_W8A16_NK}
 
 
-def timeline(op: int, M: int, N: int, K: int, pdl: int = 0, copies: int = 3):
+def timeline(op: int, M: int, N: int, K: int, pdl: int = 0, copies: int = 3, math: int = -1, chunks: int = 0,
+             stages: int = 0):
     dev = torch.device("cuda", torch.cuda.current_device())
     L = capi.lib
     ws_bytes = capi.workspace_bytes(N)
@@ -37,6 +38,14 @@ def timeline(op: int, M: int, N: int, K: int, pdl: int = 0, copies: int = 3):
     props = torch.cuda.get_device_properties(dev)
     p = capi.plan(op, M, N, K, props.multi_processor_count, 0)
     p.pdl = pdl
+    if math == 2 or (math == -1 and p.math == 2 and (chunks or stages)):
+        ck = chunks or p.k_per_stage // 64
+        p.math, p.m_tile, p.consumer_warps = 2, 16, 4
+        p.k_per_stage = ck * 64
+        p.k_blocks = -(-K // p.k_per_stage)
+        p.grid = min(props.multi_processor_count, p.tiles * p.k_blocks)
+        p.stages = stages or min(24, (232448 - 1024 - 64) // (ck * 18432 + 16))
+        p.smem_bytes = 1024 + p.stages * (ck * 18432 + 16) + 64
 
     def run(W):
         st = L.fg_gemm_planned(ctypes.byref(p), x.data_ptr(), W.data_ptr(), None, C.data_ptr(), M, N, K,
@@ -46,7 +55,7 @@ def timeline(op: int, M: int, N: int, K: int, pdl: int = 0, copies: int = 3):
     for W in Ws[:-1]:
         run(W)
     torch.cuda.synchronize()
-    buf = (ctypes.c_ulonglong * (8 * p.grid))()
+    buf = (ctypes.c_ulonglong * (16 * p.grid))()
     L.fg_trace_enable(1)
     try:
         assert L.fg_trace_read(ws.data_ptr(), buf, p.grid, stream) == capi.FG_OK  # clear
@@ -54,7 +63,7 @@ def timeline(op: int, M: int, N: int, K: int, pdl: int = 0, copies: int = 3):
         assert L.fg_trace_read(ws.data_ptr(), buf, p.grid, stream) == capi.FG_OK
     finally:
         L.fg_trace_enable(0)
-    t = np.array(list(buf), dtype=np.float64).reshape(p.grid, 8)
+    t = np.array(list(buf), dtype=np.float64).reshape(p.grid, 16)
     return p, t
 
 
@@ -65,8 +74,11 @@ def main():
     ap.add_argument("--N", type=int, default=8192)
     ap.add_argument("--K", type=int, default=8192)
     ap.add_argument("--pdl", type=int, default=0)
+    ap.add_argument("--math", type=int, default=-1, help="-1: the planner's choice; 0 mma.sync; 2 tcgen05")
+    ap.add_argument("--chunks", type=int, default=0, help="weight chunks per stage (0: the planner's choice)")
+    ap.add_argument("--stages", type=int, default=0)
     a = ap.parse_args()
-    p, t = timeline(OPS[a.op], a.M, a.N, a.K, a.pdl)
+    p, t = timeline(OPS[a.op], a.M, a.N, a.K, a.pdl, math=a.math, chunks=a.chunks, stages=a.stages)
     t0 = t[:, 0].min()
     print(f"op={a.op} M={a.M} N={a.N} K={a.K} plan={p.as_dict()}")
     print(f"stages per CTA {p.tiles * p.k_blocks / p.grid:.1f}; segments per CTA {int(t[:, 6].min())}..{int(t[:, 6].max())}")
@@ -74,6 +86,11 @@ def main():
                      (4, "warp 0 math done"), (7, "all warps math done"), (5, "finisher done")]:
         v = (t[:, col] - t0) / 1e3
         print(f"  {lab:22s} min {v.min():7.2f}  med {np.median(v):7.2f}  max {v.max():7.2f} us")
+    for col, lab in [(8, "producer: waiting for a free slot"), (9, "math: waiting for a stage"), (10, "math: issuing"),
+                     (11, "epilogue: waiting for an accumulator")]:
+        v = t[:, col] / 1e3
+        if v.max() > 0:
+            print(f"  total {lab:38s} min {v.min():7.2f}  med {np.median(v):7.2f}  max {v.max():7.2f} us")
 
 
 if __name__ == "__main__":

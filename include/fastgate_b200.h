@@ -185,12 +185,14 @@ int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* sc
                    void* ws, size_t ws_bytes, fg_stream_t stream);
 
 /* ---- built-in tracer -----------------------------------------------------------
- * While enabled (process-wide), every launch records eight %globaltimer stamps (ns) per
- * CTA in a spare corner of the workspace: [0] CTA start, [1] first copy issued, [2] last
- * copy issued, [3] first stage landed, [4] warp 0 done with the last segment's math,
- * [7] all warps done with it, [5] last segment flushed, [6] number of segments.
- * fg_trace_read synchronises `stream`, copies 8*ctas values to `out` and clears them.
- * Costs one predicated branch per event when disabled. */
+ * While enabled (process-wide), every launch records sixteen 64-bit words per CTA in a
+ * spare corner of the workspace.  %globaltimer stamps (ns): [0] CTA start, [1] first copy
+ * issued, [2] last copy issued, [3] first stage landed, [4] last tensor-core op of the last
+ * segment issued, [7] last accumulator complete / read back, [5] finishers done;
+ * [6] number of segments.  Accumulated waiting time (ns): [8] producer waiting for a free
+ * slot, [9] math waiting for a stage to land, [10] math issuing, [11] epilogue waiting for an
+ * accumulator (tcgen05 kernel).  fg_trace_read synchronises `stream`, copies 16*ctas words to
+ * `out` and clears them.  Costs one predicated branch per event when disabled. */
 int fg_trace_enable(int on);
 int fg_trace_read(void* ws, unsigned long long* out, int ctas, fg_stream_t stream);
 

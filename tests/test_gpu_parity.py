@@ -375,12 +375,12 @@ def test_tracer(dev, ws):
     try:
         out_traced, _ = run_case(case, dev, ws, check_twice=False)
         p = capi.plan(case.op, case.M, case.N, case.K, 148, 232448)
-        buf = (ctypes.c_ulonglong * (8 * p.grid))()
+        buf = (ctypes.c_ulonglong * (16 * p.grid))()
         assert capi.lib.fg_trace_read(ws.ptr, buf, p.grid, gu.stream()) == capi.FG_OK
     finally:
         capi.lib.fg_trace_enable(0)
     assert np.array_equal(out_plain, out_traced)
-    t = np.array(list(buf), dtype=np.uint64).reshape(p.grid, 8)
+    t = np.array(list(buf), dtype=np.uint64).reshape(p.grid, 16)
     assert (t[:, 0] > 0).all() and (t[:, 1] >= t[:, 0]).all() and (t[:, 2] >= t[:, 1]).all()
     assert (t[:, 6] >= 1).all()
     # the next plain call must find the borrowed workspace corner clean and still be right
