@@ -20,7 +20,8 @@ FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK = 0, 1, 2
 EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
     "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
-    "fg_gemm_f16_nk_push", "fg_push_wait", "fg_linear_host",
+    "fg_gemm_f16_nk_push", "fg_push_wait", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
+    "fg_group_tiles", "fg_group_destroy", "fg_linear_host",
     "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
@@ -44,6 +45,14 @@ class Peers(ctypes.Structure):
                 ("wait_flags", ctypes.c_void_p), ("wait_target", ctypes.c_ulonglong)]
 
 
+class Problem(ctypes.Structure):
+    """Mirror of fg_problem_t."""
+
+    _fields_ = [("x", ctypes.c_void_p), ("W", ctypes.c_void_p), ("C", ctypes.c_void_p),
+                ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("peer_C", ctypes.c_void_p * 8), ("n_total", ctypes.c_longlong)]
+
+
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -64,6 +73,14 @@ def _load() -> ctypes.CDLL:
     L.fg_gemm_planned.argtypes = [ctypes.POINTER(Plan), vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_f16_nk_push.argtypes = [vp, vp, i, i, i, ctypes.POINTER(Peers), vp, sz, vp]
     L.fg_push_wait.argtypes = [vp, i, ctypes.c_ulonglong, vp, vp]
+    L.fg_group_table_bytes.argtypes = [i]
+    L.fg_group_table_bytes.restype = sz
+    L.fg_group_create.argtypes = [i, ctypes.POINTER(Problem), i, ctypes.POINTER(Peers), vp, sz, ctypes.POINTER(vp)]
+    L.fg_group_run.argtypes = [vp, vp, sz, vp]
+    L.fg_group_tiles.argtypes = [vp]
+    L.fg_group_tiles.restype = ctypes.c_ulonglong
+    L.fg_group_destroy.argtypes = [vp]
+    L.fg_group_destroy.restype = None
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_trace_enable.argtypes = [i]
     L.fg_trace_read.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong), i, vp]

@@ -8,10 +8,13 @@
 #include <cstdint>
 #include <cstring>
 #include <mutex>
+#include <new>
+#include <vector>
 
 #include "../../include/fastgate_b200.h"
 #include "fg_kernels.cuh"
 #include "fg_umma.cuh"
+#include "fg_umma_group.cuh"
 #include "fg_layout.h"
 
 static_assert(FG_TILE_N == fg::kTileN, "layout mismatch");
@@ -58,6 +61,7 @@ struct DeviceInfo {
   int cc_major = 0;
   int smem_set[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
   int smem_set_umma[3] = {0, 0, 0};
+  int smem_set_group[2] = {0, 0};
 };
 
 constexpr int kMaxDevices = 64;
@@ -404,6 +408,194 @@ int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long lo
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return FG_OK;
 }
+
+// ---- grouped launch ------------------------------------------------------------------
+struct fg_group {
+  int op;
+  int count;
+  int device;
+  const fg::GroupEntry* table_dev;
+  uint32_t total_units;
+  uint32_t total_tiles;
+  int chunks, stages, grid, smem_bytes;
+  int world, rank;
+  unsigned long long* flag[8];
+};
+
+size_t fg_group_table_bytes(int count) {
+  return count > 0 ? static_cast<size_t>(count) * sizeof(fg::GroupEntry) : 0;
+}
+
+int fg_group_create(int op, const fg_problem_t* problems, int count, const fg_peers_t* peers, void* table_dev,
+                    size_t table_bytes, fg_group_t** out) {
+  if (problems == nullptr || out == nullptr || table_dev == nullptr) return FG_ERR_NULL;
+  *out = nullptr;
+  if (op != FG_OP_F16_KN && op != FG_OP_F16_NK) return FG_ERR_PLAN;
+  if (count < 1 || count > 65536) return FG_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(table_dev) & 127u) != 0 || table_bytes < fg_group_table_bytes(count))
+    return FG_ERR_WORKSPACE;
+  int world = 0, rank = 0;
+  if (peers != nullptr) {
+    world = peers->world;
+    rank = peers->rank;
+    if (world < 1 || world > fg::kMaxPeers || rank < 0 || rank >= world) return FG_ERR_PLAN;
+    for (int q = 0; q < world; ++q) {
+      if (peers->flag[q] == nullptr) return FG_ERR_NULL;
+      if ((reinterpret_cast<uintptr_t>(peers->flag[q]) & 7u) != 0) return FG_ERR_ALIGN;
+    }
+  }
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != FG_OK) return st;
+  int dev_index = 0;
+  cudaError_t e = cudaGetDevice(&dev_index);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  for (int i = 0; i < count; ++i) {
+    const fg_problem_t& q = problems[i];
+    if (q.x == nullptr || q.W == nullptr) return FG_ERR_NULL;
+    if (q.M <= 0 || q.M > 16 || q.N <= 0 || q.K <= 0 || (q.N % 128) != 0 || (q.K % 128) != 0) return FG_ERR_SHAPE;
+    if (!aligned16(q.x) || !aligned16(q.W)) return FG_ERR_ALIGN;
+    if (world == 0) {
+      if (q.C == nullptr) return FG_ERR_NULL;
+      if (!aligned16(q.C)) return FG_ERR_ALIGN;
+    } else {
+      if (q.n_total != static_cast<long long>(world) * q.N) return FG_ERR_SHAPE;
+      for (int r = 0; r < world; ++r) {
+        if (q.peer_C[r] == nullptr) return FG_ERR_NULL;
+        if (!aligned16(q.peer_C[r])) return FG_ERR_ALIGN;
+      }
+    }
+  }
+  // stage size: as large as still leaves every CTA at least six stages (see fg_plan)
+  const int sms = dev->sm_count < FG_MAX_GRID ? dev->sm_count : FG_MAX_GRID;
+  int chunks = 4;
+  long long units = 0;
+  for (;; chunks >>= 1) {
+    units = 0;
+    for (int i = 0; i < count; ++i)
+      units += static_cast<long long>(problems[i].N / 128) * ((problems[i].K + chunks * 64 - 1) / (chunks * 64));
+    if (chunks == 1 || units >= 6LL * sms) break;
+  }
+  const int grid = static_cast<int>(units < sms ? units : sms);
+  if (units * grid >= (1LL << 31)) return FG_ERR_SHAPE;
+  const int stage_bytes = chunks * fg_chunk_bytes(op, 16);
+  int stages = (dev->smem_optin - 1024 - 64) / (stage_bytes + 16);
+  if (stages > FG_MAX_STAGES) stages = FG_MAX_STAGES;
+  if (stages < 2) return FG_ERR_PLAN;
+
+  std::vector<fg::GroupEntry> host(count);
+  uint32_t unit = 0, tile = 0;
+  for (int i = 0; i < count; ++i) {
+    const fg_problem_t& q = problems[i];
+    fg::GroupEntry& en = host[i];
+    std::memset(&en, 0, sizeof(en));
+    if (op == FG_OP_F16_KN)
+      st = encode_2d(&en.tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q.W, q.N, q.K, 64, 64);
+    else
+      st = encode_2d(&en.tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q.W, q.K, q.N, 64, 128);
+    if (st != FG_OK) return st;
+    if ((st = encode_2d(&en.tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q.x, q.K, q.M, 64, 16)) != FG_OK) return st;
+    en.C = static_cast<__half*>(q.C);
+    for (int r = 0; r < world; ++r) en.peer_C[r] = static_cast<__half*>(q.peer_C[r]);
+    en.ldc = world ? q.n_total : q.N;
+    en.col0 = world ? rank * q.N : 0;
+    en.M = q.M;
+    en.N = q.N;
+    en.K = q.K;
+    en.KB = static_cast<uint32_t>((q.K + chunks * 64 - 1) / (chunks * 64));
+    en.tiles = static_cast<uint32_t>(q.N / 128);
+    en.unit_begin = unit;
+    en.tile_begin = tile;
+    unit += en.tiles * en.KB;
+    tile += en.tiles;
+  }
+  e = cudaMemcpy(table_dev, host.data(), fg_group_table_bytes(count), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  fg_group* grp = new (std::nothrow) fg_group();
+  if (grp == nullptr) return FG_ERR_CUDA;
+  grp->op = op;
+  grp->count = count;
+  grp->device = dev_index;
+  grp->table_dev = static_cast<const fg::GroupEntry*>(table_dev);
+  grp->total_units = unit;
+  grp->total_tiles = tile;
+  grp->chunks = chunks;
+  grp->stages = stages;
+  grp->grid = grid;
+  grp->smem_bytes = fg_umma_smem_bytes(op, chunks, stages);
+  grp->world = world;
+  grp->rank = rank;
+  for (int q = 0; q < 8; ++q) grp->flag[q] = (q < world) ? peers->flag[q] : nullptr;
+  *out = grp;
+  return FG_OK;
+}
+
+int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t stream) {
+  if (grp == nullptr) return FG_ERR_NULL;
+  if (ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0) return FG_ERR_WORKSPACE;
+  if (ws_bytes < FG_WS_TICKETS_OFFSET + 4 * static_cast<size_t>(grp->total_tiles)) return FG_ERR_WORKSPACE;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != FG_OK) return st;
+  int dev_index = -1;
+  if (cudaGetDevice(&dev_index) != cudaSuccess || dev_index != grp->device) return FG_ERR_NO_DEVICE;
+  using GroupFn = void (*)(const fg::GParams);
+  GroupFn kern = grp->op == FG_OP_F16_KN ? fg::fg_umma_group_kernel<fg::kOpF16KN> : fg::fg_umma_group_kernel<fg::kOpF16NK>;
+  int& set = dev->smem_set_group[grp->op == FG_OP_F16_NK];
+  if (grp->smem_bytes > set) {
+    const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, grp->smem_bytes);
+    if (e != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    set = grp->smem_bytes;
+  }
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  fg::GParams g;
+  g.table = grp->table_dev;
+  g.count = grp->count;
+  g.total_units = grp->total_units;
+  g.partials = reinterpret_cast<float*>(wsb + FG_WS_HEADER_BYTES);
+  g.tickets = reinterpret_cast<unsigned int*>(wsb + FG_WS_TICKETS_OFFSET);
+  g.status = reinterpret_cast<int*>(wsb);
+  g.trace = nullptr;
+  if (g_trace.load(std::memory_order_relaxed) && grp->grid <= kTraceFirstCta)
+    g.trace = reinterpret_cast<unsigned long long*>(wsb + FG_WS_HEADER_BYTES +
+                                                    static_cast<size_t>(kTraceFirstCta) * 2 * FG_WS_PARTIAL_TILE_BYTES);
+  g.chunks_per_stage = grp->chunks;
+  g.stages = grp->stages;
+  g.world = grp->world;
+  g.rank = grp->rank;
+  for (int q = 0; q < 8; ++q) g.peer_flag[q] = grp->flag[q];
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grp->grid);
+  cfg.blockDim = dim3(fg::kUmmaThreads);
+  cfg.dynamicSmemBytes = grp->smem_bytes;
+  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
+unsigned long long fg_group_tiles(const fg_group_t* grp) { return grp ? grp->total_tiles : 0; }
+
+void fg_group_destroy(fg_group_t* grp) { delete grp; }
 
 int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev, void* C_host,
                    void* x_stage_dev, void* C_stage_dev, int M, int N, int K, void* ws,

@@ -175,6 +175,39 @@ int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, 
 int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long long target, void* ws,
                  fg_stream_t stream);
 
+/* ---- grouped launch: many independent problems, one kernel ---------------------------
+ * count problems C_i[M_i,N_i] = x_i[M_i,K_i] . W_i^T (fp16, M_i <= 16, the usual 128
+ * contract; op = FG_OP_F16_NK or FG_OP_F16_KN for all) run as ONE persistent launch: the
+ * stages of all problems form one work list, so launch cost, DRAM ramp and the tail of split
+ * tiles are paid once per group instead of once per problem.  For projections whose inputs do
+ * not depend on each other (the DiT linear stack of the benchmark); layers that feed each
+ * other stay separate calls.  No counterpart in the reference (one launch per operator).
+ *
+ * fg_group_create builds the tensor maps and uploads the problem table to table_dev (caller
+ * owned device memory, 128-byte aligned, fg_group_table_bytes(count)); it synchronises (one
+ * cudaMemcpy).  Pointers and shapes are frozen in the group; the data behind them may change
+ * between runs.  With peers != NULL (world, rank and flag[] are used) every problem is one
+ * rank's N-shard: finished tiles are pushed into peer_C[r] + column rank*N of every rank and
+ * counter [rank] of every rank grows by fg_group_tiles() per run (see fg_gemm_f16_nk_push).
+ * fg_group_run only launches (workspace as for the other entry points, with room for
+ * fg_group_tiles() counters). */
+typedef struct fg_problem_t {
+  const void* x;       /* [M, K] fp16 */
+  const void* W;       /* [N, K] (NK) or [K, N] (KN) fp16 */
+  void* C;             /* [M, N] fp16; ignored when pushing */
+  int M, N, K;
+  void* peer_C[8];     /* pushing: full output [M, n_total] of every rank, as mapped here */
+  long long n_total;   /* pushing: world * N */
+} fg_problem_t;
+typedef struct fg_group fg_group_t;
+
+size_t fg_group_table_bytes(int count);
+int fg_group_create(int op, const fg_problem_t* problems, int count, const fg_peers_t* peers,
+                    void* table_dev, size_t table_bytes, fg_group_t** out);
+int fg_group_run(const fg_group_t* group, void* ws, size_t ws_bytes, fg_stream_t stream);
+unsigned long long fg_group_tiles(const fg_group_t* group);
+void fg_group_destroy(fg_group_t* group);
+
 /* ---- end-to-end convenience (HOST pointers) ---------------------------------
  * x_host and C_host are host buffers (pinned for full speed); W_dev, scales_dev,
  * x_stage_dev (M*K fp16) and C_stage_dev (M*N fp16) are device buffers the caller
