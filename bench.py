@@ -40,8 +40,8 @@ if ROOT not in sys.path:
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 N_WEIGHT_COPIES = 4
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean over the five launches of one
-# step, from the ncu capture summarised in profiles/fg_streamk_kernel__bt_sweep__ncu_full.md
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 140.1e6
+# step, from the ncu capture summarised in profiles/bt_sweep__ncu_full.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 138.9e6
 
 
 def parse_args():
