@@ -21,7 +21,7 @@ EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
     "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
     "fg_gemm_f16_nk_push", "fg_push_wait", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
-    "fg_group_tiles", "fg_group_destroy", "fg_linear_host",
+    "fg_group_tiles", "fg_group_destroy", "fg_quantize_rows_w8", "fg_linear_host",
     "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
@@ -81,6 +81,7 @@ def _load() -> ctypes.CDLL:
     L.fg_group_tiles.restype = ctypes.c_ulonglong
     L.fg_group_destroy.argtypes = [vp]
     L.fg_group_destroy.restype = None
+    L.fg_quantize_rows_w8.argtypes = [vp, vp, vp, i, i, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_trace_enable.argtypes = [i]
     L.fg_trace_read.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong), i, vp]

@@ -15,6 +15,7 @@
 #include "fg_kernels.cuh"
 #include "fg_umma.cuh"
 #include "fg_umma_group.cuh"
+#include "fg_quant.cuh"
 #include "fg_layout.h"
 
 static_assert(FG_TILE_N == fg::kTileN, "layout mismatch");
@@ -596,6 +597,22 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
 unsigned long long fg_group_tiles(const fg_group_t* grp) { return grp ? grp->total_tiles : 0; }
 
 void fg_group_destroy(fg_group_t* grp) { delete grp; }
+
+int fg_quantize_rows_w8(const void* W, int8_t* W8, void* scales, int N, int K, fg_stream_t stream) {
+  if (W == nullptr || W8 == nullptr || scales == nullptr) return FG_ERR_NULL;
+  if (N <= 0 || K <= 0 || (K % 8) != 0) return FG_ERR_SHAPE;
+  if (!aligned16(W) || (reinterpret_cast<uintptr_t>(W8) & 7u) != 0 || (reinterpret_cast<uintptr_t>(scales) & 1u) != 0)
+    return FG_ERR_ALIGN;
+  fg::fg_quantize_rows_kernel<<<N, fg::kQuantThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(W), W8, static_cast<__half*>(scales), K);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
 
 int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev, void* C_host,
                    void* x_stage_dev, void* C_stage_dev, int M, int N, int K, void* ws,

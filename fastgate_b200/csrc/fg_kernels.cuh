@@ -374,12 +374,10 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
   for (; it < n_it; ++it) {
     const int s = it % S;
     const uint32_t use = it / S;
-    const unsigned long long tw0 = trace ? globaltimer_ns() : 0;
     if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
       dead = true;
       break;
     }
-    if (trace) trace[8] += globaltimer_ns() - tw0;  // waiting for a free slot
     const int nch = stage_chunks(kb);
     mbar_arrive_expect_tx(bar_base + 8 * s, nch * cbytes);
     issue_w(s, tile, kb, nch);

@@ -1,0 +1,68 @@
+// Per-output-channel int8 quantiser: the producer of the (W8, scales) pair that
+// fastgemv_int8 / fg_gemm_w8a16_nk consume.  The reference has no quantiser (its int8 GEMV is
+// fed hand-made int8 data, script/fastgemv-int8.py:5-11); the container types it sketches for
+// quantised weights are in backend/cuda/hk/utility.cuh:13-46.
+//
+//   scale[n] = fp16( max_k |W[n,k]| / 127 )        (1 if the row is all zero)
+//   W8[n,k]  = clamp( rint( W[n,k] / float(scale[n]) ), -127, 127 )
+//
+// Dividing by the rounded fp16 scale (not the exact one) makes W8 * scale the closest
+// representable reconstruction for the scale that is actually stored.  One CTA per weight
+// row; the row is read twice (the second time from L2) and written once: HBM-bound.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace fg {
+
+constexpr int kQuantThreads = 256;
+
+__global__ void __launch_bounds__(kQuantThreads) fg_quantize_rows_kernel(const __half* __restrict__ W,
+                                                                         int8_t* __restrict__ W8,
+                                                                         __half* __restrict__ scales, int K) {
+  const size_t row = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(W + row * K);  // 8 halves per vector
+  const int nvec = K >> 3;
+  // pass 1: row maximum of |w|; for non-negative halves the bit pattern orders like the value
+  uint32_t amax_bits = 0;
+  for (int v = threadIdx.x; v < nvec; v += kQuantThreads) {
+    const uint4 q = __ldg(src + v);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t lo = w[i] & 0x7fffu, hi = (w[i] >> 16) & 0x7fffu;
+      amax_bits = max(amax_bits, max(lo, hi));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, off));
+  __shared__ uint32_t warp_max[kQuantThreads / 32];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax_bits;
+  __syncthreads();
+  amax_bits = 0;
+#pragma unroll
+  for (int i = 0; i < kQuantThreads / 32; ++i) amax_bits = max(amax_bits, warp_max[i]);
+  const float amax = __half2float(__ushort_as_half(static_cast<unsigned short>(amax_bits)));
+  const __half scale_h = (amax > 0.f) ? __float2half_rn(__fdiv_rn(amax, 127.f)) : __float2half_rn(1.f);
+  const float scale = __half2float(scale_h);
+  if (threadIdx.x == 0) scales[row] = scale_h;
+  // pass 2: quantise (round to nearest even), 8 int8 per 8-byte store
+  uint2* dst = reinterpret_cast<uint2*>(W8 + row * K);
+  for (int v = threadIdx.x; v < nvec; v += kQuantThreads) {
+    const uint4 q = __ldg(src + v);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t out[2] = {0, 0};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h2 = *reinterpret_cast<const __half2*>(&w[i]);
+      int a = __float2int_rn(__fdiv_rn(__low2float(h2), scale));
+      int b = __float2int_rn(__fdiv_rn(__high2float(h2), scale));
+      a = min(127, max(-127, a));
+      b = min(127, max(-127, b));
+      out[i >> 1] |= (static_cast<uint32_t>(a & 0xff) | (static_cast<uint32_t>(b & 0xff) << 8)) << ((i & 1) * 16);
+    }
+    dst[v] = make_uint2(out[0], out[1]);
+  }
+}
+
+}  // namespace fg

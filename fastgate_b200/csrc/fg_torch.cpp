@@ -177,6 +177,22 @@ int64_t workspace_status(int64_t device) {
   return v;
 }
 
+// W[N,K] fp16 -> (W8[N,K] int8, scales[N] fp16), one scale per output channel.
+std::pair<at::Tensor, at::Tensor> quantize_int8(at::Tensor W) {
+  check_tensor(W, "weight", at::kHalf);
+  if (W.dim() != 2 || (W.size(1) % 8) != 0) throw std::invalid_argument("fastgate_b200: weight [N,K] with K % 8 == 0 expected");
+  const c10::cuda::CUDAGuard guard(W.device());
+  at::Tensor W8 = at::empty(W.sizes(), W.options().dtype(at::kChar));
+  at::Tensor scales = at::empty({W.size(0)}, W.options());
+  if (W.numel() == 0) return {W8, scales};
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(W.get_device()).stream();
+  const int st = fg_quantize_rows_w8(W.data_ptr(), static_cast<int8_t*>(W8.data_ptr()), scales.data_ptr(),
+                                     static_cast<int>(W.size(0)), static_cast<int>(W.size(1)),
+                                     reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+  return {W8, scales};
+}
+
 // cuBLAS comparators of the reference (backend/cuda/hk/hgemm.cu:29-74, hgemm_tr.cu:30-75):
 // library calls, kept only so that scripts which import them keep working.
 void hgemm(at::Tensor A, at::Tensor B, at::Tensor C) {
@@ -223,6 +239,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("rank"), py::arg("n_total"), py::arg("wait_flag_ptr") = 0, py::arg("wait_target") = 0);
   m.def("push_wait", &push_wait, py::arg("flag_ptr"), py::arg("world"), py::arg("target"), py::arg("device"));
   m.def("workspace_status", &workspace_status, py::arg("device"));
+  m.def("quantize_int8", &quantize_int8, py::arg("W"),
+        "W[N,K] fp16 -> (W8 int8, scales fp16): symmetric, one scale per output channel, for fastgemv_int8");
   m.def("launch_count", []() { return fg_launch_count(); });
   m.def("version", []() { return std::string(fg_version()); });
 }

@@ -233,12 +233,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fg_umma_group_kernel(const GP
       for (int it = pre; it < n_it; ++it) {
         const int s = it % S;
         const uint32_t use = it / S;
-        const unsigned long long tw0 = trace ? globaltimer_ns() : 0;
         if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
           dead = true;
           break;
         }
-        if (trace) trace[8] += globaltimer_ns() - tw0;
         acquire(cw);
         const int nch = stage_chunks(cw);
         mbar_arrive_expect_tx(bar_base + 8 * s, nch * cbytes);

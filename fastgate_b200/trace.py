@@ -86,7 +86,7 @@ def main():
                      (4, "warp 0 math done"), (7, "all warps math done"), (5, "finisher done")]:
         v = (t[:, col] - t0) / 1e3
         print(f"  {lab:22s} min {v.min():7.2f}  med {np.median(v):7.2f}  max {v.max():7.2f} us")
-    for col, lab in [(8, "producer: waiting for a free slot"), (9, "math: waiting for a stage"), (10, "math: issuing"),
+    for col, lab in [(9, "math: waiting for a stage"), (10, "math: issuing"),
                      (11, "epilogue: waiting for an accumulator")]:
         v = t[:, col] / 1e3
         if v.max() > 0:

@@ -208,6 +208,13 @@ int fg_group_run(const fg_group_t* group, void* ws, size_t ws_bytes, fg_stream_t
 unsigned long long fg_group_tiles(const fg_group_t* group);
 void fg_group_destroy(fg_group_t* group);
 
+/* ---- int8 weight producer ----------------------------------------------------------------
+ * Per-output-channel symmetric quantiser for fg_gemm_w8a16_nk: W[N,K] fp16 -> W8[N,K] int8
+ * and scales[N] fp16 with scale[n] = fp16(max_k|W[n,k]| / 127) (1 for an all-zero row) and
+ * W8 = clamp(rint(W / scale), -127, 127).  K % 8 == 0.  The reference has no quantiser (its
+ * int8 GEMV is fed hand-made data, script/fastgemv-int8.py:5-11). */
+int fg_quantize_rows_w8(const void* W, int8_t* W8, void* scales, int N, int K, fg_stream_t stream);
+
 /* ---- end-to-end convenience (HOST pointers) ---------------------------------
  * x_host and C_host are host buffers (pinned for full speed); W_dev, scales_dev,
  * x_stage_dev (M*K fp16) and C_stage_dev (M*N fp16) are device buffers the caller
@@ -222,9 +229,8 @@ int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* sc
  * spare corner of the workspace.  %globaltimer stamps (ns): [0] CTA start, [1] first copy
  * issued, [2] last copy issued, [3] first stage landed, [4] last tensor-core op of the last
  * segment issued, [7] last accumulator complete / read back, [5] finishers done;
- * [6] number of segments.  Accumulated waiting time (ns): [8] producer waiting for a free
- * slot, [9] math waiting for a stage to land, [10] math issuing, [11] epilogue waiting for an
- * accumulator (tcgen05 kernel).  fg_trace_read synchronises `stream`, copies 16*ctas words to
+ * [6] number of segments.  Accumulated waiting time (ns, tcgen05 kernel): [9] math waiting for a stage to land, [10] math issuing, [11] epilogue waiting for an
+ * accumulator.  fg_trace_read synchronises `stream`, copies 16*ctas words to
  * `out` and clears them.  Costs one predicated branch per event when disabled. */
 int fg_trace_enable(int on);
 int fg_trace_read(void* ws, unsigned long long* out, int ctas, fg_stream_t stream);

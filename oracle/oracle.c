@@ -265,3 +265,28 @@ int fgo_ref_splitk_bt(int M, int N, int K) {
   }
   return BZ;
 }
+
+/* Per-output-channel int8 quantiser (no counterpart in the reference; restated here so that the
+ * CUDA quantiser can be checked bit for bit): scale[n] = fp16(max|W[n,:]| / 127), 1 for an
+ * all-zero row; W8 = clamp(rint(W / float(scale)), -127, 127), ties to even. */
+#include <math.h>
+void fgo_quantize_rows_w8(const uint16_t* W, int8_t* W8, uint16_t* scales, int N, int K) {
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    const uint16_t* w = W + (size_t)n * K;
+    float amax = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const float a = fabsf(h2f(w[k]));
+      if (a > amax) amax = a;
+    }
+    const uint16_t sh = amax > 0.f ? f2h(amax / 127.f) : f2h(1.f);
+    const float s = h2f(sh);
+    scales[n] = sh;
+    for (int k = 0; k < K; ++k) {
+      float q = nearbyintf(h2f(w[k]) / s);
+      if (q > 127.f) q = 127.f;
+      if (q < -127.f) q = -127.f;
+      W8[(size_t)n * K + k] = (int8_t)q;
+    }
+  }
+}

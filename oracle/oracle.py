@@ -144,6 +144,16 @@ def gemm_w8a16_nk(x, W8, scales=None) -> np.ndarray:
     return C
 
 
+def quantize_rows_w8(W):
+    """W[N,K] fp16 -> (W8 int8, scales fp16), per-output-channel symmetric."""
+    W = _h(W)
+    N, K = W.shape
+    W8 = np.empty((N, K), np.int8)
+    scales = np.empty(N, np.float16)
+    lib().fgo_quantize_rows_w8(_p(W), _p(W8), _p(scales), N, K)
+    return W8, scales
+
+
 def ref_splitk_bt(M: int, N: int, K: int) -> int:
     return int(lib().fgo_ref_splitk_bt(M, N, K))
 

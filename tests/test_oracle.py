@@ -104,3 +104,21 @@ def test_a_dropped_k_block_is_caught():
 def test_reference_splitk_choice(M, N, K, bz):
     """hk/edgemm.cu:287-305, values worked out by hand from the thresholds."""
     assert o.ref_splitk_bt(M, N, K) == bz
+
+
+def test_quantiser_restatement():
+    rng = np.random.default_rng(3)
+    W = (rng.standard_normal((32, 512)) / 20).astype(np.float16)
+    W[5] = 0                                  # all-zero row: scale 1, zeros
+    W[6, 0] = np.float16(3.0)                 # the row maximum maps to +-127
+    q, s = o.quantize_rows_w8(W)
+    assert q.dtype == np.int8 and s.dtype == np.float16
+    assert int(q.min()) >= -127 and int(q.max()) <= 127
+    assert float(s[5]) == 1.0 and not q[5].any()
+    assert abs(int(q[6, 0])) == 127
+    # reconstruction error is at most half a quantisation step (plus the fp16 rounding of the scale)
+    err = np.abs(q.astype(np.float32) * s[:, None].astype(np.float32) - W.astype(np.float32))
+    assert (err <= 0.51 * s[:, None].astype(np.float32) + 1e-6).all()
+    # independent numpy restatement
+    sf = s.astype(np.float32)[:, None]
+    assert np.array_equal(q, np.clip(np.rint(W.astype(np.float32) / sf), -127, 127).astype(np.int8))
