@@ -371,9 +371,11 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
   }
   int it = pre;
   issued = pre;
-  for (; it < n_it; ++it) {
-    const int s = it % S;
-    const uint32_t use = it / S;
+  // ring slot and its use count advance by increments: this loop is single-threaded and on the
+  // critical path of the ring, a runtime division per stage would show up in the call time
+  int s = (pre == S) ? 0 : pre;
+  uint32_t use = (pre == S) ? 1u : 0u;
+  for (; it < n_it; ++it, s = (s + 1 == S) ? 0 : s + 1, use += (s == 0)) {
     if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
       dead = true;
       break;
@@ -601,9 +603,13 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
 
     // stages of this segment that belong to this warp: CTA-local index == warp (mod ncw)
     const int first = it0 + ((warp - it0 % ncw) + ncw) % ncw;
-    for (int it = first; it < it0 + len && !dead; it += ncw) {
-      const int s = it % S;
-      const uint32_t use = it / S;
+    int s = first % S;
+    uint32_t use = first / S;
+    for (int it = first; it < it0 + len && !dead; it += ncw, s += ncw) {
+      if (s >= S) {  // stages % warps == 0: the slot index wraps exactly
+        s -= S;
+        ++use;
+      }
       bool ok = mbar_wait_bounded(bar_base + 8 * s, use & 1, kWaitBudgetNs);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {

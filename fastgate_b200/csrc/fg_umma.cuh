@@ -182,6 +182,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       int it0 = 0;
       uint32_t sg = 0;
       bool dead = false;
+      int s = 0;        // ring slot and phase of the next stage, advanced by increments
+      uint32_t ph = 0;
       while (u < ue && !dead) {
         const uint32_t tile = u / KB;
         const int kb0 = static_cast<int>(u - tile * KB);
@@ -195,10 +197,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         // Even and odd k16 steps accumulate into two separate TMEM tiles: consecutive MMAs
         // then do not wait for each other's accumulator; the epilogue adds the two.
         const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT);
-        for (int it = it0; it < it0 + len; ++it) {
-          const int s = it % S;
+        for (int it = it0; it < it0 + len; ++it, s = (s + 1 == S) ? 0 : s + 1, ph ^= (s == 0)) {
           const unsigned long long tw0 = trace ? globaltimer_ns() : 0;
-          if (!mbar_wait_bounded(bar_base + 8 * s, (it / S) & 1, kWaitBudgetNs)) {
+          if (!mbar_wait_bounded(bar_base + 8 * s, ph, kWaitBudgetNs)) {
             dead = true;
             break;
           }

@@ -230,9 +230,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fg_umma_group_kernel(const GP
       }
       bool dead = false;
       int issued = pre;
-      for (int it = pre; it < n_it; ++it) {
-        const int s = it % S;
-        const uint32_t use = it / S;
+      int s = (pre == S) ? 0 : pre;
+      uint32_t use = (pre == S) ? 1u : 0u;
+      for (int it = pre; it < n_it; ++it, s = (s + 1 == S) ? 0 : s + 1, use += (s == 0)) {
         if (!mbar_wait_bounded(bar_base + 8 * (S + s), (use & 1) ^ 1, kWaitBudgetNs)) {
           dead = true;
           break;
@@ -364,6 +364,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fg_umma_group_kernel(const GP
       int it0 = 0;
       uint32_t sg = 0;
       bool dead = false;
+      int s = 0;
+      uint32_t ph = 0;
       while (u < ue && !dead) {
         const int kb0 = static_cast<int>(c.kb);
         const int len = static_cast<int>((c.KB - c.kb) < (ue - u) ? (c.KB - c.kb) : (ue - u));
@@ -375,10 +377,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fg_umma_group_kernel(const GP
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT);
-        for (int it = it0; it < it0 + len; ++it) {
-          const int s = it % S;
+        for (int it = it0; it < it0 + len; ++it, s = (s + 1 == S) ? 0 : s + 1, ph ^= (s == 0)) {
           const unsigned long long tw0 = trace ? globaltimer_ns() : 0;
-          if (!mbar_wait_bounded(bar_base + 8 * s, (it / S) & 1, kWaitBudgetNs)) {
+          if (!mbar_wait_bounded(bar_base + 8 * s, ph, kWaitBudgetNs)) {
             dead = true;
             break;
           }
