@@ -21,7 +21,7 @@ EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
     "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
     "fg_gemm_f16_nk_push", "fg_push_wait", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
-    "fg_group_tiles", "fg_group_destroy", "fg_quantize_rows_w8", "fg_linear_host",
+    "fg_group_tiles", "fg_group_destroy", "fg_quantize_rows_w8", "fg_gemm_fused", "fg_linear_host",
     "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
@@ -43,6 +43,15 @@ class Peers(ctypes.Structure):
     _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("n_total", ctypes.c_longlong),
                 ("C", ctypes.c_void_p * 8), ("flag", ctypes.c_void_p * 8),
                 ("wait_flags", ctypes.c_void_p), ("wait_target", ctypes.c_ulonglong)]
+
+
+class Epilogue(ctypes.Structure):
+    """Mirror of fg_epilogue_t."""
+
+    _fields_ = [("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("act", ctypes.c_int)]
+
+
+ACT = {"none": 0, "gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3}
 
 
 class Problem(ctypes.Structure):
@@ -82,6 +91,7 @@ def _load() -> ctypes.CDLL:
     L.fg_group_destroy.argtypes = [vp]
     L.fg_group_destroy.restype = None
     L.fg_quantize_rows_w8.argtypes = [vp, vp, vp, i, i, vp]
+    L.fg_gemm_fused.argtypes = [i, vp, vp, vp, vp, i, i, i, ctypes.POINTER(Epilogue), vp, sz, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_trace_enable.argtypes = [i]
     L.fg_trace_read.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong), i, vp]

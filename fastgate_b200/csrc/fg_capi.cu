@@ -24,6 +24,9 @@ static_assert(FG_CHUNK_W_BYTES == fg::kChunkWBytes, "layout mismatch");
 static_assert(FG_MAX_CONSUMER_WARPS == fg::kMaxConsumerWarps, "layout mismatch");
 static_assert(int(FG_ERR_TIMEOUT) == int(fg::kStatusTimeout), "status mismatch");
 static_assert(int(FG_ERR_PLAN) == int(fg::kStatusBadLaunch), "status mismatch");
+static_assert(int(FG_ACT_GELU_ERF) == int(fg::kActGeluErf) && int(FG_ACT_GELU_TANH) == int(fg::kActGeluTanh) &&
+                  int(FG_ACT_SILU) == int(fg::kActSilu),
+              "activation code mismatch");
 static_assert(int(FG_OP_F16_KN) == int(fg::kOpF16KN) && int(FG_OP_F16_NK) == int(fg::kOpF16NK) &&
                   int(FG_OP_W8A16_NK) == int(fg::kOpW8A16NK),
               "op code mismatch");
@@ -189,7 +192,7 @@ int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const
 
 int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
                 const void* scales, void* C, int M, int N, int K, void* ws, cudaStream_t stream,
-                const fg_peers_t* peers = nullptr) {
+                const fg_peers_t* peers = nullptr, const fg_epilogue_t* ep = nullptr) {
   const int op = pl.op;
   const int chunks = pl.k_per_stage / fg_chunk_k(op);
   KernelFn kern = nullptr;
@@ -226,6 +229,9 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.stages = pl.stages;
   p.consumer_warps = pl.consumer_warps;
   p.pdl = pl.pdl ? 1 : 0;
+  p.bias = ep ? static_cast<const __half*>(ep->bias) : nullptr;
+  p.residual = nullptr;
+  p.act = ep ? ep->act : 0;
   p.world = 0;
   p.rank = 0;
   p.col0 = 0;
@@ -256,6 +262,8 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     if (st != FG_OK) return st;
     p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * N;
     p.M = mp;
+    if (ep != nullptr && ep->residual != nullptr)
+      p.residual = static_cast<const __half*>(ep->residual) + static_cast<size_t>(m0) * N;
     if (peers != nullptr)
       for (int q = 0; q < peers->world; ++q)
         p.peer_C[q] = static_cast<__half*>(peers->C[q]) + static_cast<size_t>(m0) * peers->n_total;
@@ -614,6 +622,25 @@ int fg_quantize_rows_w8(const void* W, int8_t* W8, void* scales, int N, int K, f
   return FG_OK;
 }
 
+int fg_gemm_fused(int op, const void* x, const void* W, const void* scales, void* C, int M, int N, int K,
+                  const fg_epilogue_t* ep, void* ws, size_t ws_bytes, fg_stream_t stream) {
+  if (op < FG_OP_F16_KN || op > FG_OP_W8A16_NK) return FG_ERR_PLAN;
+  int st = check_common(x, W, C, M, N, K, ws, ws_bytes);
+  if (st != FG_OK) return st;
+  if (ep != nullptr) {
+    if (ep->act < FG_ACT_NONE || ep->act > FG_ACT_SILU) return FG_ERR_PLAN;
+    if ((reinterpret_cast<uintptr_t>(ep->bias) & 1u) != 0 || (reinterpret_cast<uintptr_t>(ep->residual) & 1u) != 0)
+      return FG_ERR_ALIGN;
+  }
+  if (scales != nullptr && (reinterpret_cast<uintptr_t>(scales) & 3u) != 0) return FG_ERR_ALIGN;
+  DeviceInfo* dev = nullptr;
+  if ((st = device_info(&dev)) != FG_OK) return st;
+  fg_plan_t pl;
+  if ((st = fg_plan(op, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+  return run_planned(pl, dev, x, W, op == FG_OP_W8A16_NK ? scales : nullptr, C, M, N, K, ws,
+                     reinterpret_cast<cudaStream_t>(stream), nullptr, ep);
+}
+
 int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev, void* C_host,
                    void* x_stage_dev, void* C_stage_dev, int M, int N, int K, void* ws,
                    size_t ws_bytes, fg_stream_t stream) {
@@ -706,6 +733,9 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   p.stages = pl.stages;
   p.consumer_warps = pl.consumer_warps;
   p.pdl = 0;
+  p.bias = nullptr;
+  p.residual = nullptr;
+  p.act = 0;
   p.world = 0;
   p.rank = 0;
   p.col0 = 0;

@@ -45,6 +45,7 @@ constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait, th
 
 enum { kOpF16KN = 0, kOpF16NK = 1, kOpW8A16NK = 2 };
 enum { kStatusOk = 0, kStatusTimeout = 6, kStatusBadLaunch = 7 };
+enum { kActNone = 0, kActGeluErf = 1, kActGeluTanh = 2, kActSilu = 3 };
 
 template <int OP>
 struct OpTraits;
@@ -78,6 +79,11 @@ struct KParams {
   int stages;
   int consumer_warps;
   int pdl;                   // 1: launched with programmatic stream serialization
+  // Fused epilogue, applied in fp32 before the single rounding to fp16:
+  //   out = act(acc * scale + bias[n]) + residual[m, n]
+  const __half* bias;        // [N] or nullptr
+  const __half* residual;    // [M, N] (this call's rows and columns) or nullptr
+  int act;                   // kActNone, kActGeluErf, kActGeluTanh, kActSilu
   // Fused all-gather ("push") of an N-sharded layer: when world > 0 the output tile is stored
   // into the full [M, ldc] output of every rank at column col0 + n, and each finished tile
   // bumps every rank's arrival counter.  Plain stores and atomics over NVLink peer mappings.
@@ -238,13 +244,33 @@ __device__ __forceinline__ uint32_t cta_of_unit(uint32_t u, uint32_t total, uint
   return c;
 }
 
-// Scale (int8 op), round and store two adjacent outputs of row m.
+// bias, activation and residual of one output element (fp32).
+__device__ __forceinline__ float apply_act(float v, int act) {
+  switch (act) {
+    case kActGeluErf: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+    case kActGeluTanh: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    case kActSilu: return v / (1.f + expf(-v));
+    default: return v;
+  }
+}
+__device__ __forceinline__ float epilogue1(const KParams& p, int m, int n, float v) {
+  if (p.bias != nullptr) v += __half2float(p.bias[n]);
+  v = apply_act(v, p.act);
+  if (p.residual != nullptr) v += __half2float(p.residual[static_cast<size_t>(m) * p.N + n]);
+  return v;
+}
+
+// Scale (int8 op), fused epilogue, round and store two adjacent outputs of row m.
 template <int OP>
 __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float2 v) {
   if (OP == kOpW8A16NK && p.scales != nullptr) {
     const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(p.scales + n));
     v.x *= sc.x;
     v.y *= sc.y;
+  }
+  if (p.bias != nullptr || p.residual != nullptr || p.act != kActNone) {
+    v.x = epilogue1(p, m, n, v.x);
+    v.y = epilogue1(p, m, n + 1, v.y);
   }
   const __half2 h = __floats2half2_rn(v.x, v.y);
   if (p.world == 0) {

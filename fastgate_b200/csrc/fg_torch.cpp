@@ -177,6 +177,61 @@ int64_t workspace_status(int64_t device) {
   return v;
 }
 
+// Linear layer with a fused epilogue: C = act(x . W^T * scales + bias) + residual.
+// layout "nk": W[N,K] (fp16, or int8 with optional scales); "kn": W[K,N] fp16.
+void linear_fused(at::Tensor x, at::Tensor W, at::Tensor C, c10::optional<at::Tensor> scales,
+                  c10::optional<at::Tensor> bias, c10::optional<at::Tensor> residual, const std::string& act,
+                  const std::string& layout) {
+  int act_code;
+  if (act == "none") act_code = FG_ACT_NONE;
+  else if (act == "gelu" || act == "gelu_erf") act_code = FG_ACT_GELU_ERF;
+  else if (act == "gelu_tanh") act_code = FG_ACT_GELU_TANH;
+  else if (act == "silu") act_code = FG_ACT_SILU;
+  else throw std::invalid_argument("fastgate_b200: act must be none, gelu, gelu_tanh or silu");
+  if (layout != "nk" && layout != "kn") throw std::invalid_argument("fastgate_b200: layout must be nk or kn");
+  const bool int8w = W.scalar_type() == at::kChar;
+  if (int8w && layout == "kn") throw std::invalid_argument("fastgate_b200: int8 weights are stored NxK");
+  const int op = layout == "kn" ? FG_OP_F16_KN : (int8w ? FG_OP_W8A16_NK : FG_OP_F16_NK);
+  check_tensor(x, "activation", at::kHalf);
+  check_tensor(W, "weight", int8w ? at::kChar : at::kHalf);
+  check_tensor(C, "output", at::kHalf);
+  if (x.dim() != 2 || W.dim() != 2) throw std::runtime_error("fastgate_b200: activation and weight must be 2-D");
+  const int64_t M = x.size(0), K = x.size(1);
+  const int64_t N = (op == FG_OP_F16_KN) ? W.size(1) : W.size(0);
+  if (((op == FG_OP_F16_KN) ? W.size(0) : W.size(1)) != K) throw std::runtime_error("fastgate_b200: activation and weight disagree on K");
+  if (C.numel() != M * N) throw std::runtime_error("fastgate_b200: output must hold M*N elements");
+  fg_epilogue_t ep = {nullptr, nullptr, act_code};
+  const void* sp = nullptr;
+  if (scales.has_value() && scales->defined()) {
+    if (!int8w) throw std::runtime_error("fastgate_b200: scales only apply to int8 weights");
+    check_tensor(*scales, "scales", at::kHalf);
+    if (scales->numel() != N) throw std::runtime_error("fastgate_b200: scales must hold N elements");
+    sp = scales->data_ptr();
+  }
+  if (bias.has_value() && bias->defined()) {
+    check_tensor(*bias, "bias", at::kHalf);
+    if (bias->numel() != N) throw std::runtime_error("fastgate_b200: bias must hold N elements");
+    ep.bias = bias->data_ptr();
+  }
+  if (residual.has_value() && residual->defined()) {
+    check_tensor(*residual, "residual", at::kHalf);
+    if (residual->numel() != M * N) throw std::runtime_error("fastgate_b200: residual must hold M*N elements");
+    ep.residual = residual->data_ptr();
+  }
+  if (M == 0) return;
+  if ((N % 128) != 0 || (K % 128) != 0) raise(FG_ERR_SHAPE, op != FG_OP_F16_KN);
+  const c10::cuda::CUDAGuard guard(x.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
+  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  int st;
+  {
+    pybind11::gil_scoped_release nogil;
+    st = fg_gemm_fused(op, x.data_ptr(), W.data_ptr(), sp, C.data_ptr(), M, N, K, &ep, ws.buf.data_ptr(), ws.bytes,
+                       reinterpret_cast<fg_stream_t>(stream));
+  }
+  if (st != FG_OK) raise(st, op != FG_OP_F16_KN);
+}
+
 // W[N,K] fp16 -> (W8[N,K] int8, scales[N] fp16), one scale per output channel.
 std::pair<at::Tensor, at::Tensor> quantize_int8(at::Tensor W) {
   check_tensor(W, "weight", at::kHalf);
@@ -239,6 +294,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("rank"), py::arg("n_total"), py::arg("wait_flag_ptr") = 0, py::arg("wait_target") = 0);
   m.def("push_wait", &push_wait, py::arg("flag_ptr"), py::arg("world"), py::arg("target"), py::arg("device"));
   m.def("workspace_status", &workspace_status, py::arg("device"));
+  m.def("linear_fused", &linear_fused, py::arg("x"), py::arg("W"), py::arg("C"), py::arg("scales") = py::none(),
+        py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("act") = "none", py::arg("layout") = "nk",
+        "C = act(x . W^T * scales + bias) + residual in one kernel (fp32 until the final rounding)");
   m.def("quantize_int8", &quantize_int8, py::arg("W"),
         "W[N,K] fp16 -> (W8 int8, scales fp16): symmetric, one scale per output channel, for fastgemv_int8");
   m.def("launch_count", []() { return fg_launch_count(); });

@@ -86,6 +86,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(bool a_mn_major) {
 // One output element of row m, column n (scale, round, store; push-aware like store_out2).
 template <int OP>
 __device__ __forceinline__ void store_out1(const KParams& p, int m, int n, float v) {
+  if (p.bias != nullptr || p.residual != nullptr || p.act != kActNone) v = epilogue1(p, m, n, v);
   const __half h = __float2half_rn(v);
   if (p.world == 0) {
     p.C[static_cast<size_t>(m) * p.N + n] = h;

@@ -208,6 +208,22 @@ int fg_group_run(const fg_group_t* group, void* ws, size_t ws_bytes, fg_stream_t
 unsigned long long fg_group_tiles(const fg_group_t* group);
 void fg_group_destroy(fg_group_t* group);
 
+/* ---- fused epilogue ----------------------------------------------------------------------
+ * The reference has no fused operator (no bias, activation or residual anywhere in
+ * backend/cuda); at 10-25 us per call a separate elementwise kernel costs as much as the
+ * GEMV itself, so the linear layers of its stated use (DiT / LLM inference) want
+ *     C = act(x . W^T * scale + bias[n]) + residual[m, n]
+ * evaluated in fp32 and rounded once.  Any of bias, residual may be NULL; ep == NULL is the
+ * plain product.  op = FG_OP_*; scales only for FG_OP_W8A16_NK. */
+enum { FG_ACT_NONE = 0, FG_ACT_GELU_ERF = 1, FG_ACT_GELU_TANH = 2, FG_ACT_SILU = 3 };
+typedef struct fg_epilogue_t {
+  const void* bias;      /* [N] fp16 */
+  const void* residual;  /* [M, N] fp16, added after the activation */
+  int act;               /* FG_ACT_* */
+} fg_epilogue_t;
+int fg_gemm_fused(int op, const void* x, const void* W, const void* scales, void* C, int M, int N, int K,
+                  const fg_epilogue_t* ep, void* ws, size_t ws_bytes, fg_stream_t stream);
+
 /* ---- int8 weight producer ----------------------------------------------------------------
  * Per-output-channel symmetric quantiser for fg_gemm_w8a16_nk: W[N,K] fp16 -> W8[N,K] int8
  * and scales[N] fp16 with scale[n] = fp16(max_k|W[n,k]| / 127) (1 for an all-zero row) and

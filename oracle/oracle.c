@@ -290,3 +290,18 @@ void fgo_quantize_rows_w8(const uint16_t* W, int8_t* W8, uint16_t* scales, int N
     }
   }
 }
+
+/* Fused epilogue of a linear layer (no counterpart in the reference, which has no fused op):
+ * out = act(acc + bias[n]) + residual[m,n], in fp32; act: 0 none, 1 GELU (erf), 2 GELU (tanh), 3 SiLU. */
+void fgo_epilogue(float* C32, const uint16_t* bias, const uint16_t* residual, int act, int M, int N) {
+  for (int m = 0; m < M; ++m)
+    for (int n = 0; n < N; ++n) {
+      float v = C32[(size_t)m * N + n];
+      if (bias) v += h2f(bias[n]);
+      if (act == 1) v = 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+      else if (act == 2) v = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+      else if (act == 3) v = v / (1.f + expf(-v));
+      if (residual) v += h2f(residual[(size_t)m * N + n]);
+      C32[(size_t)m * N + n] = v;
+    }
+}

@@ -144,6 +144,16 @@ def gemm_w8a16_nk(x, W8, scales=None) -> np.ndarray:
     return C
 
 
+def epilogue(C32, bias=None, residual=None, act: int = 0) -> np.ndarray:
+    """act(C32 + bias) + residual on a copy of C32 (fp32); act: 0 none, 1 gelu-erf, 2 gelu-tanh, 3 silu."""
+    out = np.ascontiguousarray(C32, dtype=np.float32).copy()
+    M, N = out.shape
+    b = _p(_h(bias).reshape(-1)) if bias is not None else None
+    r = _p(_h(residual).reshape(M, N)) if residual is not None else None
+    lib().fgo_epilogue(_p(out), b, r, int(act), M, N)
+    return out
+
+
 def quantize_rows_w8(W):
     """W[N,K] fp16 -> (W8 int8, scales fp16), per-output-channel symmetric."""
     W = _h(W)
