@@ -559,6 +559,41 @@ def run_other_workload(args):
             extra["grouped"] = True
         except Exception as e:
             sys.stderr.write(f"rank {rank}: grouped launch unavailable ({e})\n")
+        # The same weights wired as a stack whose layers DO feed each other (qkv -> out + residual
+        # -> up + bias, gelu -> down + residual, block after block; the attention between qkv and
+        # out is left out, out reads the first 3072 columns of qkv): one cooperative launch per
+        # pass, to set beside per_layer_launches, which is what such a stack costs call by call.
+        if world == 1:
+            try:
+                from fastgate_b200.chain import LayerChain
+
+                h = xs[0].clone()
+                c_bias = (torch.randn(12288, device=dev, generator=g) * 0.1).to(torch.float16)
+                c_res = xs[1].clone()  # a fixed residual keeps the magnitudes of 160 chained layers bounded
+                spec, prev = [], -1
+                for b in range(len(layers) // 4):
+                    wq, wo, wu, wd = (layers[4 * b + j].w for j in range(4))
+                    qkv = torch.empty(16, 9216, dtype=torch.float16, device=dev)
+                    h1 = torch.empty(16, 3072, dtype=torch.float16, device=dev)
+                    up = torch.empty(16, 12288, dtype=torch.float16, device=dev)
+                    h2 = torch.empty(16, 3072, dtype=torch.float16, device=dev)
+                    base = len(spec)
+                    spec += [dict(x=h, W=wq, C=qkv, dep=prev),
+                             dict(x=qkv[:, :3072], W=wo, C=h1, dep=base, residual=c_res),
+                             dict(x=h1, W=wu, C=up, dep=base + 1, bias=c_bias, act="gelu_tanh"),
+                             dict(x=up, W=wd, C=h2, dep=base + 2, residual=c_res)]
+                    h, prev = h2, base + 3
+                chain = LayerChain(spec)
+                ms_chain, _ = _graph_time(chain.run, args.steps, args.warmup, world, stream, not args.no_graph)
+                if chain.status() != 0:
+                    raise RuntimeError("chain kernel reported a timeout")
+                extra["dependent_chain"] = {
+                    "ms_per_step": ms_chain / args.steps, "unit": "GB/s",
+                    "value": sum(c.algorithmic_bytes for c in cases_all) / (ms_chain / args.steps) / 1e6,
+                    "us_per_layer": ms_chain / args.steps * 1e3 / len(spec),
+                    "what": "every layer reads the previous layer's output; one cooperative launch per pass"}
+            except Exception as e:
+                sys.stderr.write(f"dependent chain unavailable ({e})\n")
         clocks = sampler.stop() if sampler else None
         steps_done = args.steps
         ms_step = ms / steps_done

@@ -21,7 +21,8 @@ EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
     "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
     "fg_gemm_f16_nk_push", "fg_push_wait", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
-    "fg_group_tiles", "fg_group_destroy", "fg_quantize_rows_w8", "fg_gemm_fused", "fg_linear_host",
+    "fg_group_tiles", "fg_group_destroy", "fg_chain_table_bytes", "fg_chain_create", "fg_chain_workspace_bytes",
+    "fg_chain_run", "fg_chain_grid", "fg_chain_trace_offset", "fg_chain_destroy", "fg_quantize_rows_w8", "fg_gemm_fused", "fg_linear_host",
     "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
@@ -62,6 +63,16 @@ class Problem(ctypes.Structure):
                 ("peer_C", ctypes.c_void_p * 8), ("n_total", ctypes.c_longlong)]
 
 
+class Layer(ctypes.Structure):
+    """Mirror of fg_layer_t."""
+
+    _fields_ = [("x", ctypes.c_void_p), ("W", ctypes.c_void_p), ("C", ctypes.c_void_p),
+                ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+                ("ldx", ctypes.c_longlong), ("ldc", ctypes.c_longlong), ("ldr", ctypes.c_longlong),
+                ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("act", ctypes.c_int), ("dep", ctypes.c_int)]
+
+
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
@@ -90,6 +101,17 @@ def _load() -> ctypes.CDLL:
     L.fg_group_tiles.restype = ctypes.c_ulonglong
     L.fg_group_destroy.argtypes = [vp]
     L.fg_group_destroy.restype = None
+    L.fg_chain_table_bytes.argtypes = [i]
+    L.fg_chain_table_bytes.restype = sz
+    L.fg_chain_create.argtypes = [i, ctypes.POINTER(Layer), i, vp, sz, ctypes.POINTER(vp)]
+    L.fg_chain_workspace_bytes.argtypes = [vp]
+    L.fg_chain_workspace_bytes.restype = sz
+    L.fg_chain_run.argtypes = [vp, vp, sz, vp]
+    L.fg_chain_grid.argtypes = [vp]
+    L.fg_chain_trace_offset.argtypes = [vp]
+    L.fg_chain_trace_offset.restype = sz
+    L.fg_chain_destroy.argtypes = [vp]
+    L.fg_chain_destroy.restype = None
     L.fg_quantize_rows_w8.argtypes = [vp, vp, vp, i, i, vp]
     L.fg_gemm_fused.argtypes = [i, vp, vp, vp, vp, i, i, i, ctypes.POINTER(Epilogue), vp, sz, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]

@@ -15,6 +15,7 @@
 #include "fg_kernels.cuh"
 #include "fg_umma.cuh"
 #include "fg_umma_group.cuh"
+#include "fg_umma_chain.cuh"
 #include "fg_quant.cuh"
 #include "fg_layout.h"
 
@@ -66,6 +67,7 @@ struct DeviceInfo {
   int smem_set[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
   int smem_set_umma[3] = {0, 0, 0};
   int smem_set_group[2] = {0, 0};
+  int smem_set_chain[2] = {0, 0};
 };
 
 constexpr int kMaxDevices = 64;
@@ -101,11 +103,12 @@ int device_info(DeviceInfo** out) {
 
 // 2-D row-major tensor: `inner` contiguous elements per row, `rows` rows, 128B swizzle.
 int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base,
-              uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows) {
+              uint64_t inner, uint64_t rows, uint32_t box_inner, uint32_t box_rows,
+              uint64_t row_stride_elems = 0) {
   EncodeTiledFn enc = get_encoder();
   if (enc == nullptr) return FG_ERR_CUDA;
   const cuuint64_t gdim[2] = {inner, rows};
-  const cuuint64_t gstride[1] = {inner * static_cast<uint64_t>(elem_bytes)};
+  const cuuint64_t gstride[1] = {(row_stride_elems ? row_stride_elems : inner) * static_cast<uint64_t>(elem_bytes)};
   const cuuint32_t box[2] = {box_inner, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(tm, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr,
@@ -119,6 +122,16 @@ int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const voi
 }
 
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const fg::KParams);
+
+// Stages beyond the first ring-full whose weights a CTA asks into L2 while it waits for the
+// previous kernel of the stream (programmatic dependent launch): about FG_L2_PREFETCH_BYTES per
+// CTA.  Measured on the 8192 x 8192 sweep: 64-128 KB per CTA takes 2-3 % off a call, 256 KB and
+// more cost time (the requests compete with the last loads of the kernel that is draining).
+int l2_prefetch_stages(int chunks) {
+  const int stage_w = chunks * 16384;  // every op moves 16 KB of weights per chunk
+  const int n = FG_L2_PREFETCH_BYTES / stage_w;
+  return n > 0 ? n : 1;
+}
 
 KernelFn pick_kernel(int op, int m_tile) {
   switch (op * 2 + (m_tile == 16)) {
@@ -173,7 +186,7 @@ int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const
   cfg.gridDim = dim3(pl.grid);
   // tcgen05 kernel: fixed warp roles; mma.sync kernel: consumers + one copy-issuing warp +
   // m_tile/4 warps that finish split tiles
-  cfg.blockDim = dim3(pl.math == 2 ? fg::kUmmaThreads : (pl.consumer_warps + 1 + pl.m_tile / 4) * 32);
+  cfg.blockDim = dim3(pl.math == 2 ? fg::kUmmaThreads : (pl.consumer_warps + 1 + 2 * (pl.m_tile / 4)) * 32);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -229,6 +242,7 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.stages = pl.stages;
   p.consumer_warps = pl.consumer_warps;
   p.pdl = pl.pdl ? 1 : 0;
+  p.l2_prefetch = pl.pdl ? l2_prefetch_stages(chunks) : 0;
   p.bias = ep ? static_cast<const __half*>(ep->bias) : nullptr;
   p.residual = nullptr;
   p.act = ep ? ep->act : 0;
@@ -585,7 +599,7 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
   for (int q = 0; q < 8; ++q) g.peer_flag[q] = grp->flag[q];
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grp->grid);
-  cfg.blockDim = dim3(fg::kUmmaThreads);
+  cfg.blockDim = dim3(fg::kUmmaGroupThreads);
   cfg.dynamicSmemBytes = grp->smem_bytes;
   cfg.stream = reinterpret_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attr[1];
@@ -605,6 +619,190 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
 unsigned long long fg_group_tiles(const fg_group_t* grp) { return grp ? grp->total_tiles : 0; }
 
 void fg_group_destroy(fg_group_t* grp) { delete grp; }
+
+// ---- dependent layer chain -------------------------------------------------------------
+struct fg_chain {
+  int op;
+  int count;
+  int device;
+  const fg::ChainEntry* table_dev;
+  uint32_t total_tiles;
+  int chunks, stages, grid, smem_bytes;
+  size_t off_tickets, off_done, off_trace, ws_bytes;
+};
+
+size_t fg_chain_table_bytes(int count) {
+  return count > 0 ? static_cast<size_t>(count) * sizeof(fg::ChainEntry) : 0;
+}
+
+int fg_chain_create(int op, const fg_layer_t* layers, int count, void* table_dev, size_t table_bytes,
+                    fg_chain_t** out) {
+  if (layers == nullptr || out == nullptr || table_dev == nullptr) return FG_ERR_NULL;
+  *out = nullptr;
+  if (op != FG_OP_F16_KN && op != FG_OP_F16_NK) return FG_ERR_PLAN;
+  if (count < 1 || count > 65536) return FG_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(table_dev) & 127u) != 0 || table_bytes < fg_chain_table_bytes(count))
+    return FG_ERR_WORKSPACE;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != FG_OK) return st;
+  int dev_index = 0;
+  cudaError_t e = cudaGetDevice(&dev_index);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  for (int i = 0; i < count; ++i) {
+    const fg_layer_t& q = layers[i];
+    if (q.x == nullptr || q.W == nullptr || q.C == nullptr) return FG_ERR_NULL;
+    if (q.M <= 0 || q.M > 16 || q.N <= 0 || q.K <= 0 || (q.N % 128) != 0 || (q.K % 128) != 0) return FG_ERR_SHAPE;
+    if (q.ldx < 0 || q.ldc < 0 || q.ldr < 0) return FG_ERR_SHAPE;
+    if ((q.ldx != 0 && q.ldx < q.K) || (q.ldc != 0 && q.ldc < q.N) || (q.ldr != 0 && q.ldr < q.N)) return FG_ERR_SHAPE;
+    if (!aligned16(q.x) || !aligned16(q.W) || !aligned16(q.C) || (q.ldx % 8) != 0 || (q.ldc % 8) != 0)
+      return FG_ERR_ALIGN;
+    if (q.residual != nullptr && (reinterpret_cast<uintptr_t>(q.residual) & 1u) != 0) return FG_ERR_ALIGN;
+    if (q.bias != nullptr && (reinterpret_cast<uintptr_t>(q.bias) & 1u) != 0) return FG_ERR_ALIGN;
+    if (q.act < FG_ACT_NONE || q.act > FG_ACT_SILU) return FG_ERR_PLAN;
+    if (q.dep < -1 || q.dep >= i) return FG_ERR_PLAN;
+  }
+  // stage size: as large as still leaves every CTA about six stages per layer on average
+  const int sms = dev->sm_count < FG_MAX_GRID ? dev->sm_count : FG_MAX_GRID;
+  int chunks = 4;
+  long long units = 0, max_units = 0;
+  for (;; chunks >>= 1) {
+    units = 0;
+    max_units = 0;
+    for (int i = 0; i < count; ++i) {
+      const long long u = static_cast<long long>(layers[i].N / 128) * ((layers[i].K + chunks * 64 - 1) / (chunks * 64));
+      units += u;
+      max_units = u > max_units ? u : max_units;
+    }
+    if (chunks == 1 || units >= 6LL * sms * count) break;
+  }
+  const int grid = static_cast<int>(max_units < sms ? max_units : sms);
+  if (max_units * grid >= (1LL << 31)) return FG_ERR_SHAPE;
+  const int stage_bytes = chunks * fg_chunk_bytes(op, 16);
+  int stages = (dev->smem_optin - 1024 - 96) / (stage_bytes + 16);  // 32 bytes more than the plain kernel: two finisher teams
+  if (stages > FG_MAX_STAGES) stages = FG_MAX_STAGES;
+  if (stages < 2) return FG_ERR_PLAN;
+
+  std::vector<fg::ChainEntry> host(count);
+  uint32_t tile = 0;
+  for (int i = 0; i < count; ++i) {
+    const fg_layer_t& q = layers[i];
+    fg::ChainEntry& en = host[i];
+    std::memset(&en, 0, sizeof(en));
+    if (op == FG_OP_F16_KN)
+      st = encode_2d(&en.tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q.W, q.N, q.K, 64, 64);
+    else
+      st = encode_2d(&en.tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q.W, q.K, q.N, 64, 128);
+    if (st != FG_OK) return st;
+    st = encode_2d(&en.tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q.x, q.K, q.M, 64, 16, static_cast<uint64_t>(q.ldx));
+    if (st != FG_OK) return st;
+    en.C = static_cast<__half*>(q.C);
+    en.bias = static_cast<const __half*>(q.bias);
+    en.residual = static_cast<const __half*>(q.residual);
+    en.ldc = q.ldc ? q.ldc : q.N;
+    en.ldr = q.ldr ? q.ldr : q.N;
+    en.M = q.M;
+    en.N = q.N;
+    en.K = q.K;
+    en.act = q.act;
+    en.dep = q.dep;
+    en.KB = static_cast<uint32_t>((q.K + chunks * 64 - 1) / (chunks * 64));
+    en.tiles = static_cast<uint32_t>(q.N / 128);
+    en.tile_begin = tile;
+    tile += en.tiles;
+  }
+  e = cudaMemcpy(table_dev, host.data(), fg_chain_table_bytes(count), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  fg_chain* ch = new (std::nothrow) fg_chain();
+  if (ch == nullptr) return FG_ERR_CUDA;
+  ch->op = op;
+  ch->count = count;
+  ch->device = dev_index;
+  ch->table_dev = static_cast<const fg::ChainEntry*>(table_dev);
+  ch->total_tiles = tile;
+  ch->chunks = chunks;
+  ch->stages = stages;
+  ch->grid = grid;
+  ch->smem_bytes = fg_umma_smem_bytes(op, chunks, stages) + 32;
+  // header | grid x 4 partial tiles | one ticket per tile | one counter per layer | timestamps
+  ch->off_tickets = FG_WS_HEADER_BYTES + static_cast<size_t>(grid) * 4 * FG_WS_PARTIAL_TILE_BYTES;
+  ch->off_done = (ch->off_tickets + 4 * static_cast<size_t>(tile) + 255) & ~static_cast<size_t>(255);
+  ch->off_trace = (ch->off_done + 4 * static_cast<size_t>(count) + 255) & ~static_cast<size_t>(255);
+  ch->ws_bytes = (ch->off_trace + 64 * static_cast<size_t>(count) * grid + 255) & ~static_cast<size_t>(255);
+  *out = ch;
+  return FG_OK;
+}
+
+size_t fg_chain_workspace_bytes(const fg_chain_t* ch) { return ch ? ch->ws_bytes : 0; }
+
+int fg_chain_run(const fg_chain_t* ch, void* ws, size_t ws_bytes, fg_stream_t stream) {
+  if (ch == nullptr) return FG_ERR_NULL;
+  if (ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255u) != 0 || ws_bytes < ch->ws_bytes) return FG_ERR_WORKSPACE;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != FG_OK) return st;
+  int dev_index = -1;
+  if (cudaGetDevice(&dev_index) != cudaSuccess || dev_index != ch->device) return FG_ERR_NO_DEVICE;
+  using ChainFn = void (*)(const fg::CParams);
+  ChainFn kern = ch->op == FG_OP_F16_KN ? fg::fg_umma_chain_kernel<fg::kOpF16KN> : fg::fg_umma_chain_kernel<fg::kOpF16NK>;
+  int& set = dev->smem_set_chain[ch->op == FG_OP_F16_NK];
+  cudaError_t e;
+  if (ch->smem_bytes > set) {
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             ch->smem_bytes);
+    if (e != cudaSuccess) {
+      g_last_cuda = static_cast<int>(e);
+      return FG_ERR_CUDA;
+    }
+    set = ch->smem_bytes;
+  }
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  e = cudaMemsetAsync(wsb + ch->off_done, 0, 4 * static_cast<size_t>(ch->count), s);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  fg::CParams g;
+  g.table = ch->table_dev;
+  g.count = ch->count;
+  g.partials = reinterpret_cast<float*>(wsb + FG_WS_HEADER_BYTES);
+  g.tickets = reinterpret_cast<unsigned int*>(wsb + ch->off_tickets);
+  g.done = reinterpret_cast<unsigned int*>(wsb + ch->off_done);
+  g.status = reinterpret_cast<int*>(wsb);
+  g.trace = g_trace.load(std::memory_order_relaxed) ? reinterpret_cast<unsigned long long*>(wsb + ch->off_trace) : nullptr;
+  g.chunks_per_stage = ch->chunks;
+  g.stages = ch->stages;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ch->grid);
+  cfg.blockDim = dim3(fg::kUmmaThreads);
+  cfg.dynamicSmemBytes = ch->smem_bytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;  // the CTAs wait on one another: all must be resident
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, g);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
+int fg_chain_grid(const fg_chain_t* ch) { return ch ? ch->grid : 0; }
+
+size_t fg_chain_trace_offset(const fg_chain_t* ch) { return ch ? ch->off_trace : 0; }
+
+void fg_chain_destroy(fg_chain_t* ch) { delete ch; }
 
 int fg_quantize_rows_w8(const void* W, int8_t* W8, void* scales, int N, int K, fg_stream_t stream) {
   if (W == nullptr || W8 == nullptr || scales == nullptr) return FG_ERR_NULL;
@@ -733,6 +931,7 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   p.stages = pl.stages;
   p.consumer_warps = pl.consumer_warps;
   p.pdl = 0;
+  p.l2_prefetch = 0;
   p.bias = nullptr;
   p.residual = nullptr;
   p.act = 0;

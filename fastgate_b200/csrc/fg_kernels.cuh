@@ -31,6 +31,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "fg_ptx.cuh"
 
 namespace fg {
@@ -79,6 +81,7 @@ struct KParams {
   int stages;
   int consumer_warps;
   int pdl;                   // 1: launched with programmatic stream serialization
+  int l2_prefetch;           // stages beyond the first ring-full whose weights are prefetched into L2 while waiting
   // Fused epilogue, applied in fp32 before the single rounding to fp16:
   //   out = act(acc * scale + bias[n]) + residual[m, n]
   const __half* bias;        // [N] or nullptr
@@ -244,33 +247,45 @@ __device__ __forceinline__ uint32_t cta_of_unit(uint32_t u, uint32_t total, uint
   return c;
 }
 
-// bias, activation and residual of one output element (fp32).
-__device__ __forceinline__ float apply_act(float v, int act) {
+// Activation chosen at compile time, and a dispatcher that turns the runtime code into it ONCE
+// around a whole loop nest: a per-element switch costs microseconds in the single-warp tails.
+template <int ACT>
+__device__ __forceinline__ float act_fn(float v) {
+  if constexpr (ACT == kActGeluErf) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  else if constexpr (ACT == kActGeluTanh) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  else if constexpr (ACT == kActSilu) return v / (1.f + expf(-v));
+  else return v;
+}
+template <typename F>
+__device__ __forceinline__ void with_act(int act, F&& f) {
   switch (act) {
-    case kActGeluErf: return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
-    case kActGeluTanh: return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-    case kActSilu: return v / (1.f + expf(-v));
-    default: return v;
+    case kActGeluErf: f(std::integral_constant<int, kActGeluErf>{}); break;
+    case kActGeluTanh: f(std::integral_constant<int, kActGeluTanh>{}); break;
+    case kActSilu: f(std::integral_constant<int, kActSilu>{}); break;
+    default: f(std::integral_constant<int, kActNone>{}); break;
   }
 }
+
+// bias, activation and residual of one output element (fp32).
+template <int ACT>
 __device__ __forceinline__ float epilogue1(const KParams& p, int m, int n, float v) {
   if (p.bias != nullptr) v += __half2float(p.bias[n]);
-  v = apply_act(v, p.act);
+  v = act_fn<ACT>(v);
   if (p.residual != nullptr) v += __half2float(p.residual[static_cast<size_t>(m) * p.N + n]);
   return v;
 }
 
 // Scale (int8 op), fused epilogue, round and store two adjacent outputs of row m.
-template <int OP>
+template <int OP, int ACT>
 __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float2 v) {
   if (OP == kOpW8A16NK && p.scales != nullptr) {
     const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(p.scales + n));
     v.x *= sc.x;
     v.y *= sc.y;
   }
-  if (p.bias != nullptr || p.residual != nullptr || p.act != kActNone) {
-    v.x = epilogue1(p, m, n, v.x);
-    v.y = epilogue1(p, m, n + 1, v.y);
+  if (ACT != kActNone || p.bias != nullptr || p.residual != nullptr) {
+    v.x = epilogue1<ACT>(p, m, n, v.x);
+    v.y = epilogue1<ACT>(p, m, n + 1, v.y);
   }
   const __half2 h = __floats2half2_rn(v.x, v.y);
   if (p.world == 0) {
@@ -385,6 +400,27 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
       if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
     }
   }
+  // While the previous kernel drains, HBM would idle once the ring is full: ask for the next
+  // stages' weights to be brought into L2 meanwhile (they are loaded from there later).
+  if (p.l2_prefetch > 0) {
+    int t2 = tile, k2 = kb;
+    for (int i = 0; i < pre; ++i)
+      if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
+    const int last = (pre + p.l2_prefetch) < n_it ? (pre + p.l2_prefetch) : n_it;
+    for (int i = pre; i < last; ++i) {
+      const int nch = stage_chunks(k2);
+      for (int c = 0; c < nch; ++c) {
+        const int kc = k2 * k_per_stage + c * T::chunkK;
+        if constexpr (OP == kOpF16KN) {
+          tma_prefetch_l2_2d(&tmW, t2 * kTileN, kc);
+          tma_prefetch_l2_2d(&tmW, t2 * kTileN + 64, kc);
+        } else {
+          tma_prefetch_l2_2d(&tmW, kc, t2 * kTileN);
+        }
+      }
+      if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
+    }
+  }
   griddep_wait();
   if (p.wait_flags != nullptr && !wait_counters(p.wait_flags, p.wait_world, p.wait_target)) {
     // The activations never became ready.  Complete the armed stages with what is there
@@ -427,8 +463,13 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
 }
 
 // ------------------------------------ finisher ------------------------------------------
-// MT/4 warps (named barrier kFinBarrier).  They walk the same segment list as the consumers.
-// For every partial segment they wait until all consumer threads have stored their share of
+// Two teams of MT/4 warps (named barriers kFinBarrier, kFinBarrier + 1).  A CTA has at most two
+// partial segments: the tail of the tile its share starts in and the head of the tile it ends
+// in.  Team 0 takes the first partial of the CTA, team 1 the second, so that a CTA whose first
+// partial turns out to be the last contribution to its tile (a reduction of a few microseconds)
+// does not hold back the ticket of its second partial.  The teams walk the same segment list
+// as the consumers.
+// For its partial segment a team waits until all consumer threads have stored their share of
 // the partial tile; one thread publishes it (fence + ticket) and, if this CTA was the last
 // contributor of the tile, the warps add up all partials in CTA order and write C: warp w
 // takes rows 4w..4w+3, lane l columns 4l..4l+3, contributors four at a time, so every lane
@@ -441,9 +482,12 @@ __host__ __device__ constexpr int finisher_warps() { return MT / 4; }
 
 template <int OP, int MT>
 __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r, uint32_t bar_flush,
-                                             uint32_t bar_fin, volatile uint32_t* prev_slot, int fin_warp,
+                                             volatile uint32_t* prev_slot, int team, int fin_warp,
                                              int lane, unsigned long long* trace) {
   constexpr int FW = finisher_warps<MT>();
+  bar_flush += 8 * team;
+  prev_slot += team;
+  const int bar_id = kFinBarrier + team;
   const uint32_t KB = r.KB, total = r.total, G = r.G, ub = r.ub, ue = r.ue;
   uint32_t u = ub;
   uint32_t ev = 0;
@@ -453,8 +497,8 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
     const uint32_t tile = u / KB;
     const uint32_t kb0 = u - tile * KB;
     const uint32_t len = (KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u);
-    if (len != KB && !dead) {
-      bool ok = mbar_wait_bounded(bar_flush, ev & 1, kWaitBudgetNs * 4);
+    if (len != KB && ev == static_cast<uint32_t>(team) && !dead) {
+      bool ok = mbar_wait_bounded(bar_flush, 0, kWaitBudgetNs * 4);
       ok = __all_sync(0xffffffffu, ok);
       const uint32_t c_first = cta_of_unit(tile * KB, total, G);
       const uint32_t c_last = cta_of_unit(tile * KB + KB - 1, total, G);
@@ -469,7 +513,7 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
         }
         *prev_slot = prev;
       }
-      named_bar_sync(kFinBarrier, FW * 32);
+      named_bar_sync(bar_id, FW * 32);
       const uint32_t prev = *prev_slot;
       if (prev == 0xffffffffu) dead = true;
       if (prev == c_last - c_first) {
@@ -506,39 +550,41 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
                 sum[i].w += v[j][i].w;
               }
           }
+          with_act(p.act, [&](auto tag) {
+            constexpr int ACT = decltype(tag)::value;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int m = m0 + i;
-            if (m < p.M) {
-              store_out2<OP>(p, m, n0, make_float2(sum[i].x, sum[i].y));
-              store_out2<OP>(p, m, n0 + 2, make_float2(sum[i].z, sum[i].w));
+            for (int i = 0; i < 4; ++i) {
+              const int m = m0 + i;
+              if (m < p.M) {
+                store_out2<OP, ACT>(p, m, n0, make_float2(sum[i].x, sum[i].y));
+                store_out2<OP, ACT>(p, m, n0 + 2, make_float2(sum[i].z, sum[i].w));
+              }
             }
-          }
+          });
         }
         if (p.world > 0) __threadfence_system();  // this thread's stores into the other ranks' outputs
       }
-      // every finisher warp has seen this phase of bar_flush and is done with *prev_slot
-      named_bar_sync(kFinBarrier, FW * 32);
+      // every warp of the team is done with the tile's partials before the ticket is reset
+      named_bar_sync(bar_id, FW * 32);
       if (leader) {
         if (prev == c_last - c_first) {
           p.tickets[tile] = 0;  // ready for the next launch
           if (p.world > 0) signal_tile_delivered(p);
         }
-        mbar_arrive(bar_fin);
       }
-      ++ev;
     }
+    if (len != KB) ++ev;
     u += len;
   }
-  if (trace && leader) trace[5] = globaltimer_ns();  // finisher done
+  if (trace && leader) trace[5 + 8 * team] = globaltimer_ns();  // team done (slot 5: team 0, slot 13: team 1)
 }
 
-// Warp roles: [0, ncw) consume, ncw produces (TMA), ncw + 1 ... finish split tiles.
+// Warp roles: [0, ncw) consume, ncw produces (TMA), then two teams of MT/4 warps finish split tiles.
 // The int8 op is planned with at most four consumer warps, which leaves its dequantising
 // inner loop more registers.
 template <int OP, int MT>
 __host__ __device__ constexpr int streamk_max_threads() {
-  return ((OP == kOpW8A16NK ? 4 : kMaxConsumerWarps) + 1 + finisher_warps<MT>()) * 32;
+  return ((OP == kOpW8A16NK ? 4 : kMaxConsumerWarps) + 1 + 2 * finisher_warps<MT>()) * 32;
 }
 
 template <int OP, int MT>
@@ -558,14 +604,13 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
   const uint32_t ring_bytes = S * stage_bytes;
   float* red = reinterpret_cast<float*>(smem_gen + ring_bytes);
   const uint32_t red_bytes = ncw * MT * kRedStride * 4;
-  const uint32_t bar_base = smem_base + ring_bytes + red_bytes;  // full[S], empty[S], flush, fin
-  const uint32_t bar_flush = bar_base + 16 * S;     // consumers -> finisher: "my partial is stored"
-  const uint32_t bar_fin = bar_base + 16 * S + 8;   // finisher -> consumers: "previous partial handled"
+  const uint32_t bar_base = smem_base + ring_bytes + red_bytes;  // full[S], empty[S], flush[2]
+  const uint32_t bar_flush = bar_base + 16 * S;     // consumers -> team t: "my partial #t is stored"
   volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + red_bytes + 16 * S + 16);
 
   // A launch whose thread count or shared memory does not fit the parameters would index
   // shared memory out of bounds: refuse it instead (the host reads the status word).
-  if (blockDim.x != static_cast<unsigned>((ncw + 1 + finisher_warps<MT>()) * 32) ||
+  if (blockDim.x != static_cast<unsigned>((ncw + 1 + 2 * finisher_warps<MT>()) * 32) ||
       dynamic_smem_size() < 1023u + ring_bytes + red_bytes + 16u * S + 32u) {
     if (threadIdx.x == 0) atomicExch(p.status, kStatusBadLaunch);
     return;
@@ -576,6 +621,7 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
   const int nct = ncw * 32;
   unsigned long long* trace = p.trace ? p.trace + kTraceSlots * blockIdx.x : nullptr;
   if (trace && threadIdx.x == 0) trace[0] = globaltimer_ns();  // CTA start
+  if (trace && threadIdx.x == 0) trace[12] = smid();                     // which SM ran this CTA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -583,7 +629,7 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
       mbar_init(bar_base + 8 * (S + s), 1);  // empty: one arrive (the consuming warp's lane 0)
     }
     mbar_init(bar_flush, nct);
-    mbar_init(bar_fin, 1);
+    mbar_init(bar_flush + 8, nct);
     fence_mbar_init();
     fence_proxy_async();
   }
@@ -602,7 +648,9 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
     return;
   }
   if (warp > ncw) {
-    run_finisher<OP, MT>(p, range, bar_flush, bar_fin, prev_slot, warp - ncw - 1, lane, trace);
+    const int fw = warp - ncw - 1;
+    run_finisher<OP, MT>(p, range, bar_flush, prev_slot, fw / finisher_warps<MT>(), fw % finisher_warps<MT>(), lane,
+                         trace);
     return;
   }
 
@@ -670,22 +718,12 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
         myred[(m + 1) * kRedStride + n + 8] = acc[rg][j][3];
       }
     const bool whole = (len == static_cast<int>(KB));
-    if (!whole && ev >= 1) {
-      // the finisher must have seen the previous partial before the next one is announced
-      // (both sides then observe every phase of bar_flush / bar_fin); normally long done
-      bool ok = mbar_wait_bounded(bar_fin, (ev - 1) & 1, kWaitBudgetNs * 4);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok && !dead) {
-        dead = true;
-        if (lane == 0) atomicExch(p.status, kStatusTimeout);
-      }
-    }
     named_bar_sync(1, nct);
     if (trace && ctid == 0) trace[7] = globaltimer_ns();  // all warps done with the segment's math
 
     const int slot = (u == ub) ? 0 : 1;
     float* mypart = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MT * kTileN);
-    for (int e = ctid; e < MT * 64; e += nct) {
+    auto reduce_warps = [&](int e) {  // sum of the consumer warps' copies of outputs 2e, 2e+1 of the tile
       const int m = e >> 6, n2 = (e & 63) * 2;
       float2 v = make_float2(0.f, 0.f);
       for (int w = 0; w < ncw; ++w) {
@@ -693,14 +731,21 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
         v.x += a.x;
         v.y += a.y;
       }
-      if (whole) {
-        if (m < p.M) store_out2<OP>(p, m, tile * kTileN + n2, v);
-      } else {
-        *reinterpret_cast<float2*>(mypart + 2 * e) = v;
-      }
+      return v;
+    };
+    if (whole) {
+      with_act(p.act, [&](auto tag) {
+        constexpr int ACT = decltype(tag)::value;
+        for (int e = ctid; e < MT * 64; e += nct) {
+          const int m = e >> 6, n2 = (e & 63) * 2;
+          if (m < p.M) store_out2<OP, ACT>(p, m, tile * kTileN + n2, reduce_warps(e));
+        }
+      });
+    } else {
+      for (int e = ctid; e < MT * 64; e += nct) *reinterpret_cast<float2*>(mypart + 2 * e) = reduce_warps(e);
     }
     if (!whole) {
-      mbar_arrive(bar_flush);  // release: this thread's share of the partial tile is stored
+      mbar_arrive(bar_flush + 8 * ev);  // release: this thread's share of partial #ev is stored
       ++ev;
     } else if (p.world > 0) {
       __threadfence_system();  // this thread's stores into the other ranks' outputs

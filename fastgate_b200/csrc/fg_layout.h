@@ -5,6 +5,7 @@
 
 #define FG_MAX_GRID 256            /* persistent CTAs the workspace has room for        */
 #define FG_MAX_STAGES 24           /* ring depth limit                                  */
+#define FG_L2_PREFETCH_BYTES 98304 /* weights per CTA asked into L2 while it waits for the previous kernel */
 #define FG_MAX_CONSUMER_WARPS 8
 #define FG_TILE_N 128              /* output columns per tile                           */
 #define FG_CHUNK_W_BYTES 16384     /* weight bytes per chunk                            */

@@ -21,7 +21,8 @@
 namespace fg {
 
 constexpr int kUmmaMT = 16;            // token rows of the accumulator (UMMA N)
-constexpr int kUmmaThreads = (6 + kUmmaMT / 4) * 32;
+constexpr int kUmmaThreads = (6 + 2 * (kUmmaMT / 4)) * 32;   // two finisher teams (see run_finisher)
+constexpr int kUmmaGroupThreads = (6 + kUmmaMT / 4) * 32;  // grouped and chained kernels: one team
 constexpr int kUmmaChains = 2;         // independent accumulation chains per tile (summed in the epilogue)
 constexpr uint32_t kTmemCols = 64;     // 2 buffers x 2 chains x 16 columns
 
@@ -84,9 +85,9 @@ __host__ __device__ constexpr uint32_t umma_idesc(bool a_mn_major) {
 }
 
 // One output element of row m, column n (scale, round, store; push-aware like store_out2).
-template <int OP>
+template <int OP, int ACT>
 __device__ __forceinline__ void store_out1(const KParams& p, int m, int n, float v) {
-  if (p.bias != nullptr || p.residual != nullptr || p.act != kActNone) v = epilogue1(p, m, n, v);
+  if (ACT != kActNone || p.bias != nullptr || p.residual != nullptr) v = epilogue1<ACT>(p, m, n, v);
   const __half h = __float2half_rn(v);
   if (p.world == 0) {
     p.C[static_cast<size_t>(m) * p.N + n] = h;
@@ -115,11 +116,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const uint32_t bar_base = smem_base + ring_bytes;         // full[S], empty[S]
   const uint32_t bar_acc_full = bar_base + 16 * S;          // [2] MMA -> epilogue
   const uint32_t bar_acc_empty = bar_acc_full + 16;         // [2] epilogue -> MMA
-  const uint32_t bar_flush = bar_acc_empty + 16;            // epilogue -> finisher
-  const uint32_t bar_fin = bar_flush + 8;                   // finisher -> epilogue
-  const uint32_t tmem_slot = bar_fin + 8;
+  const uint32_t bar_flush = bar_acc_empty + 16;            // [2] epilogue -> finisher team
+  const uint32_t tmem_slot = bar_flush + 16;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + 16 * S + 48);
-  volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + 16 * S + 52);
+  volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + 16 * S + 52);  // [2]
 
   // refuse a launch that does not fit the parameters (see fg_streamk_kernel)
   if (blockDim.x != static_cast<unsigned>(kUmmaThreads) || dynamic_smem_size() < 1023u + ring_bytes + 16u * S + 64u) {
@@ -131,6 +131,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const int lane = threadIdx.x & 31;
   unsigned long long* trace = p.trace ? p.trace + kTraceSlots * blockIdx.x : nullptr;
   if (trace && threadIdx.x == 0) trace[0] = globaltimer_ns();
+  if (trace && threadIdx.x == 0) trace[12] = smid();                     // which SM ran this CTA
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -142,7 +143,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       mbar_init(bar_acc_empty + 8 * b, 4);   // lane 0 of each epilogue warp
     }
     mbar_init(bar_flush, 128);
-    mbar_init(bar_fin, 1);
+    mbar_init(bar_flush + 8, 128);
     fence_mbar_init();
     fence_proxy_async();
   }
@@ -167,7 +168,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     return;
   }
   if (warp >= 6) {
-    run_finisher<OP, MT>(p, range, bar_flush, bar_fin, prev_slot, warp - 6, lane, trace);
+    run_finisher<OP, MT>(p, range, bar_flush, prev_slot, (warp - 6) / finisher_warps<MT>(),
+                         (warp - 6) % finisher_warps<MT>(), lane, trace);
     return;
   }
 
@@ -285,31 +287,23 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       }
       const int n = tile * kTileN + n_in_tile;
       if (whole) {
-        float sc = 1.f;
-        (void)sc;
+        with_act(p.act, [&](auto tag) {
+          constexpr int ACT = decltype(tag)::value;
 #pragma unroll
-        for (int m = 0; m < MT; ++m)
-          if (m < p.M) store_out1<OP>(p, m, n, __uint_as_float(r[m]));
+          for (int m = 0; m < MT; ++m)
+            if (m < p.M) store_out1<OP, ACT>(p, m, n, __uint_as_float(r[m]));
+        });
         if (p.world > 0) {
           __threadfence_system();
           named_bar_sync(1, 128);
           if (threadIdx.x == 0) signal_tile_delivered(p);
         }
       } else {
-        if (ev >= 1) {
-          // the finisher must have seen the previous partial before the next one is announced
-          bool ok = mbar_wait_bounded(bar_fin, (ev - 1) & 1, kWaitBudgetNs * 4);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok && !dead) {
-            dead = true;
-            if (lane == 0) atomicExch(p.status, kStatusTimeout);
-          }
-        }
         const int slot = (u == ub) ? 0 : 1;
         float* mypart = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MT * kTileN);
 #pragma unroll
         for (int m = 0; m < MT; ++m) mypart[m * kTileN + n_in_tile] = __uint_as_float(r[m]);
-        mbar_arrive(bar_flush);
+        mbar_arrive(bar_flush + 8 * ev);
         ++ev;
       }
       if (trace && threadIdx.x == 0) trace[6] += 1;

@@ -108,7 +108,7 @@ __device__ __forceinline__ void group_signal(const GParams& g) {
 }
 
 template <int OP>
-__global__ void __launch_bounds__(kUmmaThreads, 1) fg_umma_group_kernel(const GParams g) {
+__global__ void __launch_bounds__(kUmmaGroupThreads, 1) fg_umma_group_kernel(const GParams g) {
   static_assert(OP == kOpF16KN || OP == kOpF16NK, "tcgen05 path: fp16 weights only");
   constexpr int MT = kUmmaMT;
   extern __shared__ uint8_t smem_raw[];
@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fg_umma_group_kernel(const GP
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + 16 * S + 48);
   volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + 16 * S + 52);
 
-  if (blockDim.x != static_cast<unsigned>(kUmmaThreads) || dynamic_smem_size() < 1023u + ring_bytes + 16u * S + 64u) {
+  if (blockDim.x != static_cast<unsigned>(kUmmaGroupThreads) || dynamic_smem_size() < 1023u + ring_bytes + 16u * S + 64u) {
     if (threadIdx.x == 0) atomicExch(g.status, kStatusBadLaunch);
     return;
   }

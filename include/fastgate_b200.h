@@ -208,6 +208,50 @@ int fg_group_run(const fg_group_t* group, void* ws, size_t ws_bytes, fg_stream_t
 unsigned long long fg_group_tiles(const fg_group_t* group);
 void fg_group_destroy(fg_group_t* group);
 
+/* ---- dependent layer chain: a stack of projections that feed each other, one kernel ------
+ * count layers C_i[M,N_i] = act(x_i[M,K_i] . W_i^T + bias_i) + residual_i (fp16, M <= 16, the
+ * usual 128 contract, one op for all) run in order inside ONE persistent, cooperatively
+ * launched kernel.  x_i may be the output of an earlier layer dep_i of the same chain, or a
+ * column slice of it (row stride ldx): the kernel keeps streaming the next layer's weights
+ * while the previous layer's last tiles drain and holds back only the activations, on a
+ * per-layer counter of finished tiles (bounded wait, FG_ERR_TIMEOUT in the workspace status).
+ * A launch per layer pays its fixed cost per layer; the chain pays it once.  No counterpart
+ * in the reference (one launch per operator).
+ *
+ * Rules: dep < the layer's own index (or -1: x is ready when the launch starts); a layer may
+ * overwrite a buffer only if it depends, directly or through its chain of dep, on every layer
+ * that reads that buffer; residual may alias C (in place).  fg_chain_create builds the tensor
+ * maps and uploads the layer table to table_dev (caller owned, 128-byte aligned,
+ * fg_chain_table_bytes(count)); it synchronises.  fg_chain_run enqueues one small memset
+ * (the per-layer counters) and the kernel; the workspace is the chain's own
+ * (fg_chain_workspace_bytes, 256-byte aligned, cleared once with fg_workspace_init). */
+typedef struct fg_layer_t {
+  const void* x;         /* [M, K] fp16, row stride ldx elements (0: K) */
+  const void* W;         /* [N, K] (NK) or [K, N] (KN) fp16, dense */
+  void* C;               /* [M, N] fp16, row stride ldc elements (0: N) */
+  const void* bias;      /* [N] fp16 or NULL */
+  const void* residual;  /* [M, N] fp16, row stride ldr elements (0: N), or NULL */
+  long long ldx, ldc, ldr;
+  int M, N, K;
+  int act;               /* FG_ACT_* */
+  int dep;               /* index of the layer that produces x, or -1 */
+} fg_layer_t;
+typedef struct fg_chain fg_chain_t;
+
+size_t fg_chain_table_bytes(int count);
+int fg_chain_create(int op, const fg_layer_t* layers, int count, void* table_dev, size_t table_bytes,
+                    fg_chain_t** out);
+size_t fg_chain_workspace_bytes(const fg_chain_t* chain);
+int fg_chain_run(const fg_chain_t* chain, void* ws, size_t ws_bytes, fg_stream_t stream);
+/* With fg_trace_enable(1) a run also writes eight words per layer and CTA at
+ * fg_chain_trace_offset() of the workspace, as unsigned long long [count][fg_chain_grid()][8]:
+ * timestamps (ns) of activations ready, first stage landed, last stage committed, last tile or
+ * partial handed on, last partial written, its ticket back, its reduction loaded; and the number
+ * of contributors if this CTA reduced its last split tile (else 0). */
+int fg_chain_grid(const fg_chain_t* chain);
+size_t fg_chain_trace_offset(const fg_chain_t* chain);
+void fg_chain_destroy(fg_chain_t* chain);
+
 /* ---- fused epilogue ----------------------------------------------------------------------
  * The reference has no fused operator (no bias, activation or residual anywhere in
  * backend/cuda); at 10-25 us per call a separate elementwise kernel costs as much as the
