@@ -50,7 +50,7 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
-    ap.add_argument("--workload", choices=("bt_sweep", "cfg1", "cfg3", "cfg4", "dit"), default="bt_sweep",
+    ap.add_argument("--workload", choices=("bt_sweep", "cfg1", "cfg3", "cfg4", "w4", "dit"), default="bt_sweep",
                     help="bt_sweep (default, config 2) | cfg1 edgemm_m8n128k64x4 | cfg3 fastgemv | cfg4 fastgemv_int8 | "
                          "dit: the 40-layer DiT linear stack, N-sharded over the GPUs (strong scaling)")
     ap.add_argument("--layers", type=int, default=40, help="dit: number of layers")
@@ -436,7 +436,7 @@ def run_other_workload(args):
     if name != "dit":
         if world != 1:
             raise SystemExit(f"--workload {name} is a single-GPU workload")
-        cases = {"cfg1": wl.cfg1, "cfg3": wl.cfg3, "cfg4": wl.cfg4}[name]()
+        cases = {"cfg1": wl.cfg1, "cfg3": wl.cfg3, "cfg4": wl.cfg4, "w4": wl.w4}[name]()
         copies = []  # per case: rotating weight copies beyond the L2 size
         for c in cases:
             n_rot = max(2, -(-600 * 2 ** 20 // c.weight_bytes))
@@ -454,8 +454,10 @@ def run_other_workload(args):
                 fg.edgemm_m8n128k64x4(xs[ci], w, outs[ci])
             elif c.op == wl.OP_NK:
                 fg.fastgemv(w, xs[ci], outs[ci])
-            else:
+            elif c.op == wl.OP_W8:
                 fg.fastgemv_int8(w, xs[ci], outs[ci], scs[ci])
+            else:
+                fg.fastgemv_int4(w, xs[ci], outs[ci], scs[ci])
 
         n_rot_all = max(len(c) for c in copies)
 
@@ -479,7 +481,8 @@ def run_other_workload(args):
         launches = steps_done * len(cases)
         workload = {"cfg1": "edgemm_m8n128k64x4: M=8, K=N=4096, weight KxN fp16",
                     "cfg3": "fastgemv: M=1, weight 11008x4096 and 4096x11008 fp16 (NxK)",
-                    "cfg4": "fastgemv_int8: M in {1,8}, weight int8 28672x8192 + fp16 scale per output channel"}[name]
+                    "cfg4": "fastgemv_int8: M in {1,8}, weight int8 28672x8192 + fp16 scale per output channel",
+                    "w4": "fastgemv_int4: M in {1,8,16}, weight 28672x8192 packed 4-bit + fp16 scale per 128 k"}[name]
         sharding = "single GPU"
         scaling = "weak"
         metric = "effective HBM GB/s of M<=16 fp16/int8 GEMM-GEMV"
@@ -621,7 +624,8 @@ def run_other_workload(args):
     line = {
         "metric": metric, "value": bytes_step / ms_step / 1e6, "unit": "GB/s", "n_gpus": world, "steps": steps_done,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-        "dtype": "int8 weights, f16 activations (fp32 accumulate)" if name == "cfg4" else "f16 (fp32 accumulate)",
+        "dtype": {"cfg4": "int8 weights, f16 activations (fp32 accumulate)",
+                  "w4": "int4 weights, f16 activations (fp32 accumulate)"}.get(name, "f16 (fp32 accumulate)"),
         "data": "synthetic",
         "config": {"workload": workload, "calls_per_step": n_calls, "sharding": sharding,
                    "l2": "weights rotate over more than 600 MB" if name != "dit" else "9 GB of distinct weights per pass",

@@ -14,12 +14,12 @@ LIB_PATH = os.path.join(_HERE, "libfastgate_b200.so")
 
 FG_OK, FG_ERR_SHAPE, FG_ERR_ALIGN, FG_ERR_NULL, FG_ERR_WORKSPACE = 0, 1, 2, 3, 4
 FG_ERR_CUDA, FG_ERR_TIMEOUT, FG_ERR_PLAN, FG_ERR_NO_DEVICE = 5, 6, 7, 8
-FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK = 0, 1, 2
+FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK, FG_OP_W4A16_NK = 0, 1, 2, 3
 
 # every symbol include/fastgate_b200.h declares
 EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
-    "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
+    "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_w4a16_nk", "fg_quantize_rows_w4", "fg_gemm_f16_nk_noalloc", "fg_gemm_planned",
     "fg_gemm_f16_nk_push", "fg_push_wait", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
     "fg_group_tiles", "fg_group_destroy", "fg_chain_table_bytes", "fg_chain_create", "fg_chain_workspace_bytes",
     "fg_chain_run", "fg_chain_grid", "fg_chain_trace_offset", "fg_chain_destroy", "fg_quantize_rows_w8", "fg_gemm_fused", "fg_linear_host",
@@ -89,6 +89,7 @@ def _load() -> ctypes.CDLL:
     L.fg_gemm_f16_kn.argtypes = [vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_f16_nk.argtypes = [vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_w8a16_nk.argtypes = [vp, vp, vp, vp, i, i, i, vp, sz, vp]
+    L.fg_gemm_w4a16_nk.argtypes = [vp, vp, vp, i, i, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_f16_nk_noalloc.argtypes = [vp, vp, vp, i, i, i, vp]
     L.fg_gemm_planned.argtypes = [ctypes.POINTER(Plan), vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_gemm_f16_nk_push.argtypes = [vp, vp, i, i, i, ctypes.POINTER(Peers), vp, sz, vp]
@@ -113,6 +114,7 @@ def _load() -> ctypes.CDLL:
     L.fg_chain_destroy.argtypes = [vp]
     L.fg_chain_destroy.restype = None
     L.fg_quantize_rows_w8.argtypes = [vp, vp, vp, i, i, vp]
+    L.fg_quantize_rows_w4.argtypes = [vp, vp, vp, i, i, i, vp]
     L.fg_gemm_fused.argtypes = [i, vp, vp, vp, vp, i, i, i, ctypes.POINTER(Epilogue), vp, sz, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_trace_enable.argtypes = [i]

@@ -29,7 +29,7 @@ static_assert(int(FG_ACT_GELU_ERF) == int(fg::kActGeluErf) && int(FG_ACT_GELU_TA
                   int(FG_ACT_SILU) == int(fg::kActSilu),
               "activation code mismatch");
 static_assert(int(FG_OP_F16_KN) == int(fg::kOpF16KN) && int(FG_OP_F16_NK) == int(fg::kOpF16NK) &&
-                  int(FG_OP_W8A16_NK) == int(fg::kOpW8A16NK),
+                  int(FG_OP_W8A16_NK) == int(fg::kOpW8A16NK) && int(FG_OP_W4A16_NK) == int(fg::kOpW4A16NK),
               "op code mismatch");
 
 extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin_bytes);
@@ -64,7 +64,7 @@ struct DeviceInfo {
   int sm_count = 0;
   int smem_optin = 0;
   int cc_major = 0;
-  int smem_set[3][2] = {{0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
+  int smem_set[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
   int smem_set_umma[3] = {0, 0, 0};
   int smem_set_group[2] = {0, 0};
   int smem_set_chain[2] = {0, 0};
@@ -140,7 +140,9 @@ KernelFn pick_kernel(int op, int m_tile) {
     case 2: return fg::fg_streamk_kernel<fg::kOpF16NK, 8>;
     case 3: return fg::fg_streamk_kernel<fg::kOpF16NK, 16>;
     case 4: return fg::fg_streamk_kernel<fg::kOpW8A16NK, 8>;
-    default: return fg::fg_streamk_kernel<fg::kOpW8A16NK, 16>;
+    case 5: return fg::fg_streamk_kernel<fg::kOpW8A16NK, 16>;
+    case 6: return fg::fg_streamk_kernel<fg::kOpW4A16NK, 8>;
+    default: return fg::fg_streamk_kernel<fg::kOpW4A16NK, 16>;
   }
 }
 
@@ -203,9 +205,16 @@ int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const
   return FG_OK;
 }
 
+// int4 op: scales per row and the zero point
+struct QuantArgs {
+  int groups;
+  int zero_point;
+};
+
 int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
                 const void* scales, void* C, int M, int N, int K, void* ws, cudaStream_t stream,
-                const fg_peers_t* peers = nullptr, const fg_epilogue_t* ep = nullptr) {
+                const fg_peers_t* peers = nullptr, const fg_epilogue_t* ep = nullptr,
+                const QuantArgs* qa = nullptr) {
   const int op = pl.op;
   const int chunks = pl.k_per_stage / fg_chunk_k(op);
   KernelFn kern = nullptr;
@@ -220,13 +229,20 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, W, N, K, 64, 64);
   else if (op == FG_OP_F16_NK)
     st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, W, K, N, 64, 128);
-  else
+  else if (op == FG_OP_W8A16_NK)
     st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, K, N, 128, 128);
+  else
+    st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, K / 2, N, 128, 128);  // packed nibbles
   if (st != FG_OK) return st;
 
   uint8_t* wsb = static_cast<uint8_t*>(ws);
   fg::KParams p;
   p.scales = static_cast<const __half*>(scales);
+  p.scale_groups = qa ? qa->groups : 1;
+  {
+    const unsigned int h = __half_as_ushort(__float2half_rn(1024.f + static_cast<float>(qa ? qa->zero_point : 0)));
+    p.w4_magic = h | (h << 16);
+  }
   p.partials = reinterpret_cast<float*>(wsb + FG_WS_HEADER_BYTES);
   p.tickets = reinterpret_cast<unsigned int*>(wsb + FG_WS_TICKETS_OFFSET);
   p.status = reinterpret_cast<int*>(wsb);
@@ -287,7 +303,7 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
 }
 
 int run_op(int op, const void* x, const void* W, const void* scales, void* C, int M, int N, int K,
-           void* ws, size_t ws_bytes, fg_stream_t stream) {
+           void* ws, size_t ws_bytes, fg_stream_t stream, const QuantArgs* qa = nullptr) {
   int st = check_common(x, W, C, M, N, K, ws, ws_bytes);
   if (st != FG_OK) return st;
   if (scales != nullptr && (reinterpret_cast<uintptr_t>(scales) & 3u) != 0) return FG_ERR_ALIGN;
@@ -295,7 +311,8 @@ int run_op(int op, const void* x, const void* W, const void* scales, void* C, in
   if ((st = device_info(&dev)) != FG_OK) return st;
   fg_plan_t pl;
   if ((st = fg_plan(op, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
-  return run_planned(pl, dev, x, W, scales, C, M, N, K, ws, reinterpret_cast<cudaStream_t>(stream));
+  return run_planned(pl, dev, x, W, scales, C, M, N, K, ws, reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr,
+                     qa);
 }
 
 // ---- scratch for fg_gemm_f16_nk_noalloc -------------------------------------------------
@@ -381,6 +398,26 @@ int fg_gemm_f16_nk(const void* x, const void* W, void* C, int M, int N, int K, v
 int fg_gemm_w8a16_nk(const void* x, const int8_t* W8, const void* scales, void* C, int M, int N,
                      int K, void* ws, size_t ws_bytes, fg_stream_t stream) {
   return run_op(FG_OP_W8A16_NK, x, W8, scales, C, M, N, K, ws, ws_bytes, stream);
+}
+
+int fg_gemm_w4a16_nk(const void* x, const uint8_t* W4, const void* scales, int groups, int zero_point, void* C,
+                     int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream) {
+  if (zero_point < 0 || zero_point > 15) return FG_ERR_PLAN;
+  if (K > 0 && groups != 1 && groups != K / 128) return FG_ERR_SHAPE;
+  if (scales != nullptr && groups > 1 && (reinterpret_cast<uintptr_t>(scales) & 1u) != 0) return FG_ERR_ALIGN;
+  QuantArgs qa{scales != nullptr ? groups : 1, zero_point};
+  if (groups > 1 && scales != nullptr) {
+    // group-wise scales are read two bytes at a time: only the common checks apply
+    int st = check_common(x, W4, C, M, N, K, ws, ws_bytes);
+    if (st != FG_OK) return st;
+    DeviceInfo* dev = nullptr;
+    if ((st = device_info(&dev)) != FG_OK) return st;
+    fg_plan_t pl;
+    if ((st = fg_plan(FG_OP_W4A16_NK, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+    return run_planned(pl, dev, x, W4, scales, C, M, N, K, ws, reinterpret_cast<cudaStream_t>(stream), nullptr,
+                       nullptr, &qa);
+  }
+  return run_op(FG_OP_W4A16_NK, x, W4, scales, C, M, N, K, ws, ws_bytes, stream, &qa);
 }
 
 int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const void* scales, void* C,
@@ -811,6 +848,27 @@ int fg_quantize_rows_w8(const void* W, int8_t* W8, void* scales, int N, int K, f
     return FG_ERR_ALIGN;
   fg::fg_quantize_rows_kernel<<<N, fg::kQuantThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(W), W8, static_cast<__half*>(scales), K);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
+int fg_quantize_rows_w4(const void* W, uint8_t* W4, void* scales, int groups, int N, int K, fg_stream_t stream) {
+  if (W == nullptr || W4 == nullptr || scales == nullptr) return FG_ERR_NULL;
+  if (N <= 0 || K <= 0 || (K % 128) != 0 || (groups != 1 && groups != K / 128)) return FG_ERR_SHAPE;
+  if (!aligned16(W) || (reinterpret_cast<uintptr_t>(W4) & 3u) != 0 || (reinterpret_cast<uintptr_t>(scales) & 1u) != 0)
+    return FG_ERR_ALIGN;
+  const long long segments = static_cast<long long>(N) * groups;
+  const int per_cta = fg::kQuantThreads / 32;
+  const long long grid = (segments + per_cta - 1) / per_cta;
+  if (grid > 0x7fffffffLL) return FG_ERR_SHAPE;
+  fg::fg_quantize_rows_w4_kernel<<<static_cast<unsigned int>(grid), fg::kQuantThreads, 0,
+                                   reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(W), W4, static_cast<__half*>(scales), K, K / groups, segments);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     g_last_cuda = static_cast<int>(e);

@@ -45,7 +45,7 @@ constexpr int kMaxPeers = 8;          // ranks of one NVLink box
 constexpr int kTraceSlots = 16;       // 64-bit words per CTA of the built-in tracer
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait, then give up
 
-enum { kOpF16KN = 0, kOpF16NK = 1, kOpW8A16NK = 2 };
+enum { kOpF16KN = 0, kOpF16NK = 1, kOpW8A16NK = 2, kOpW4A16NK = 3 };
 enum { kStatusOk = 0, kStatusTimeout = 6, kStatusBadLaunch = 7 };
 enum { kActNone = 0, kActGeluErf = 1, kActGeluTanh = 2, kActSilu = 3 };
 
@@ -66,10 +66,18 @@ struct OpTraits<kOpW8A16NK> {
   static constexpr int chunkK = 128;
   static constexpr int xBoxes = 2;
 };
+template <>
+struct OpTraits<kOpW4A16NK> {
+  static constexpr int chunkK = 256;      // 128 rows x 128 bytes of packed 4-bit weights
+  static constexpr int xBoxes = 4;
+};
+__host__ __device__ constexpr bool op_is_quantized(int op) { return op == kOpW8A16NK || op == kOpW4A16NK; }
 
 struct KParams {
   __half* C;                 // [M, N]
-  const __half* scales;      // [N] or nullptr (int8 op only)
+  const __half* scales;      // quantized ops: [N] per output channel, or [N, scale_groups] (int4), or nullptr
+  int scale_groups;          // int4 op: scales per row; > 1: one per 128 k, applied inside the k loop
+  uint32_t w4_magic;         // int4 op: half2(1024 + zero_point) twice
   float* partials;           // [grid][2][MT * 128]
   unsigned int* tickets;     // [tiles], zero between launches
   int* status;               // device status word
@@ -104,7 +112,7 @@ struct KParams {
 };
 
 __host__ __device__ constexpr int chunk_bytes(int op, int mt) {
-  return kChunkWBytes + (op == kOpW8A16NK ? 2 : 1) * mt * 128;
+  return kChunkWBytes + (op == kOpW4A16NK ? 4 : op == kOpW8A16NK ? 2 : 1) * mt * 128;
 }
 
 // ---- one 16 KB weight chunk against its activation tile ------------------------------
@@ -151,9 +159,104 @@ __device__ __forceinline__ void load_a_frags_f16(uint32_t wbase, int kk, int q, 
 
 template <int OP, int MT>
 __device__ __forceinline__ void consume_chunk(uint32_t wbase, uint32_t xbase, int lane,
-                                              float (&acc)[8][MT / 8][4]) {
+                                              float (&acc)[8][MT / 8][4], const KParams& p, int n0, int k0) {
   const int q = lane >> 3, r = lane & 7;
-  if constexpr (OP == kOpF16NK || OP == kOpF16KN) {
+  if constexpr (OP == kOpW4A16NK) {
+    // Packed 4-bit weight chunk [128 n][128 B = 256 k], low nibble first.  The thread with
+    // t = lane % 4 owns one 32-bit word (eight consecutive k) of its rows per 32-k piece; the
+    // word dequantises into four half2 (k, k+4), (k+1, k+5), (k+2, k+6), (k+3, k+7) that feed two
+    // k16 steps, and the activation fragment is built with the same permutation from one
+    // 16-byte shared load.  Each 128-k half of the chunk is summed into a fresh accumulator,
+    // scaled by its group's scale (group-wise scales) and added in fp32.
+    const int g = lane >> 2, t = lane & 3;
+    const int G = p.scale_groups;
+    const bool grouped = G > 1;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+      uint32_t b[4][MT / 8][4];
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc)
+#pragma unroll
+        for (int j = 0; j < MT / 8; ++j) {
+          const int c = hf * 4 + pc, m = j * 8 + g;
+          const uint32_t addr = xbase + (c >> 1) * (MT * 128) + m * 128 + (((((c & 1) * 4) + t) ^ (m & 7)) << 4);
+          uint32_t x0, x1, x2, x3;
+          lds_v4(addr, x0, x1, x2, x3);
+          b[pc][j][0] = prmt(x0, x2, 0x5410);
+          b[pc][j][1] = prmt(x0, x2, 0x7632);
+          b[pc][j][2] = prmt(x1, x3, 0x5410);
+          b[pc][j][3] = prmt(x1, x3, 0x7632);
+        }
+      __half sc[8][2];
+      if (grouped) {
+        int gi = (k0 >> 7) + hf;
+        gi = gi < G ? gi : G - 1;  // a ragged last chunk: its second half is all zero activations
+#pragma unroll
+        for (int rg = 0; rg < 8; ++rg) {
+          const __half* srow = p.scales + static_cast<size_t>(n0 + rg * 16 + g) * G + gi;
+          sc[rg][0] = __ldg(srow);
+          sc[rg][1] = __ldg(srow + 8 * static_cast<size_t>(G));
+        }
+      }
+      // Two 16-row groups at a time, and with an 8-row token tile the two k16 steps of a word in
+      // accumulators of their own: four independent MMA chains in flight either way.
+      constexpr int SP = (MT == 8) ? 2 : 1;
+#pragma unroll
+      for (int rp = 0; rp < 4; ++rp) {
+        uint32_t w[2][2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int ci = 0; ci < 2; ++ci) {
+            const int rg = rp * 2 + h, cp = hf * 2 + ci;
+            const uint32_t addr = wbase + (rg * 16 + (q & 1) * 8 + r) * 128 + ((((cp * 2) + (q >> 1)) ^ r) << 4);
+            ldsm_x4(addr, w[h][ci][0], w[h][ci][1], w[h][ci][2], w[h][ci][3]);
+          }
+        float tmp[2][SP][MT / 8][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int sp = 0; sp < SP; ++sp)
+#pragma unroll
+            for (int j = 0; j < MT / 8; ++j)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) tmp[h][sp][j][i] = 0.f;
+#pragma unroll
+        for (int ci = 0; ci < 2; ++ci)
+#pragma unroll
+          for (int ph = 0; ph < 2; ++ph) {
+            const int pc = ci * 2 + ph;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t lo[4], hi[4];  // rows g and g + 8 of this 16-row group
+              dequant_u4x8(w[h][ci][ph * 2], p.w4_magic, lo);
+              dequant_u4x8(w[h][ci][ph * 2 + 1], p.w4_magic, hi);
+#pragma unroll
+              for (int j = 0; j < MT / 8; ++j) {
+                mma_16816(tmp[h][0][j], lo[0], hi[0], lo[1], hi[1], b[pc][j][0], b[pc][j][1]);
+                mma_16816(tmp[h][SP - 1][j], lo[2], hi[2], lo[3], hi[3], b[pc][j][2], b[pc][j][3]);
+              }
+            }
+          }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int rg = rp * 2 + h;
+          const float s0 = grouped ? __half2float(sc[rg][0]) : 1.f;
+          const float s1 = grouped ? __half2float(sc[rg][1]) : 1.f;
+#pragma unroll
+          for (int j = 0; j < MT / 8; ++j) {
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) v[i] = (SP == 2) ? tmp[h][0][j][i] + tmp[h][SP - 1][j][i] : tmp[h][0][j][i];
+            acc[rg][j][0] += v[0] * s0;
+            acc[rg][j][1] += v[1] * s0;
+            acc[rg][j][2] += v[2] * s1;
+            acc[rg][j][3] += v[3] * s1;
+          }
+        }
+      }
+    }
+  } else if constexpr (OP == kOpF16NK || OP == kOpF16KN) {
     // Software pipeline over the four k16 steps: the fragments of step kk+1 are in flight
     // while the tensor-core ops of step kk issue.
     uint32_t a[2][8][4];
@@ -278,7 +381,7 @@ __device__ __forceinline__ float epilogue1(const KParams& p, int m, int n, float
 // Scale (int8 op), fused epilogue, round and store two adjacent outputs of row m.
 template <int OP, int ACT>
 __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float2 v) {
-  if (OP == kOpW8A16NK && p.scales != nullptr) {
+  if ((OP == kOpW8A16NK || (OP == kOpW4A16NK && p.scale_groups <= 1)) && p.scales != nullptr) {
     const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(p.scales + n));
     v.x *= sc.x;
     v.y *= sc.y;
@@ -366,7 +469,8 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
         tma_load_2d(dst, &tmW, full, tl * kTileN, kc, pol_w);
         tma_load_2d(dst + 8192, &tmW, full, tl * kTileN + 64, kc, pol_w);
       } else {
-        tma_load_2d(dst, &tmW, full, kc, tl * kTileN, pol_w);
+        // the weight map counts elements of its own type: two k per byte for the int4 op
+        tma_load_2d(dst, &tmW, full, OP == kOpW4A16NK ? kc >> 1 : kc, tl * kTileN, pol_w);
       }
       dst += cbytes;
     }
@@ -415,7 +519,7 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
           tma_prefetch_l2_2d(&tmW, t2 * kTileN, kc);
           tma_prefetch_l2_2d(&tmW, t2 * kTileN + 64, kc);
         } else {
-          tma_prefetch_l2_2d(&tmW, kc, t2 * kTileN);
+          tma_prefetch_l2_2d(&tmW, OP == kOpW4A16NK ? kc >> 1 : kc, t2 * kTileN);
         }
       }
       if (++k2 == static_cast<int>(KB)) { k2 = 0; ++t2; }
@@ -580,11 +684,11 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
 }
 
 // Warp roles: [0, ncw) consume, ncw produces (TMA), then two teams of MT/4 warps finish split tiles.
-// The int8 op is planned with at most four consumer warps, which leaves its dequantising
-// inner loop more registers.
+// The quantized ops are planned with at most four consumer warps (three with a 16-row tile), which
+// keeps the CTA at 384 threads or fewer and leaves their dequantising inner loops 168 registers.
 template <int OP, int MT>
 __host__ __device__ constexpr int streamk_max_threads() {
-  return ((OP == kOpW8A16NK ? 4 : kMaxConsumerWarps) + 1 + 2 * finisher_warps<MT>()) * 32;
+  return ((op_is_quantized(OP) ? (MT == 16 ? 3 : 4) : kMaxConsumerWarps) + 1 + 2 * finisher_warps<MT>()) * 32;
 }
 
 template <int OP, int MT>
@@ -697,7 +801,7 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
       nch = nch < cps ? nch : cps;
       uint32_t base = smem_base + s * stage_bytes;
       for (int c = 0; c < nch; ++c) {
-        consume_chunk<OP, MT>(base, base + kChunkWBytes, lane, acc);
+        consume_chunk<OP, MT>(base, base + kChunkWBytes, lane, acc, p, tile * kTileN, k0 + c * T::chunkK);
         base += cbytes;
       }
       __syncwarp();

@@ -19,9 +19,9 @@
 #define FG_WS_TICKETS_OFFSET (FG_WS_HEADER_BYTES + FG_WS_PARTIALS_BYTES)
 
 /* op codes mirror FG_OP_* of the public header */
-static inline int fg_chunk_k(int op) { return op == 2 ? 128 : 64; }
+static inline int fg_chunk_k(int op) { return op == 3 ? 256 : op == 2 ? 128 : 64; }
 /* activation boxes (64 k x m_tile rows, 128 B per row) that accompany one weight chunk */
-static inline int fg_x_boxes(int op) { return op == 2 ? 2 : 1; }
+static inline int fg_x_boxes(int op) { return op == 3 ? 4 : op == 2 ? 2 : 1; }
 static inline int fg_chunk_bytes(int op, int m_tile) {
   return FG_CHUNK_W_BYTES + fg_x_boxes(op) * m_tile * 128;
 }

@@ -15,7 +15,7 @@ extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin
                        fg_plan_t* out) {
   if (out == nullptr) return FG_ERR_NULL;
   std::memset(out, 0, sizeof(*out));
-  if (op < FG_OP_F16_KN || op > FG_OP_W8A16_NK) return FG_ERR_PLAN;
+  if (op < FG_OP_F16_KN || op > FG_OP_W4A16_NK) return FG_ERR_PLAN;
   if (M <= 0 || N <= 0 || K <= 0 || (N % 128) != 0 || (K % 128) != 0) return FG_ERR_SHAPE;
   if (sm_count <= 0) sm_count = 148;                 // B200
   if (smem_optin_bytes <= 0) smem_optin_bytes = 232448;  // 227 KB opt-in per CTA on sm_100
@@ -31,7 +31,8 @@ extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin
   p.tiles = N / 128;
 
   const int chunk_k = fg_chunk_k(op);
-  if (op != FG_OP_W8A16_NK && p.m_tile == 16) {
+  const bool quantized = (op == FG_OP_W8A16_NK || op == FG_OP_W4A16_NK);
+  if (!quantized && p.m_tile == 16) {
     // fp16 weights, more than 8 token rows: the tcgen05 kernel (accumulator in tensor memory,
     // no cross-warp reduction, the whole shared memory is ring).  Its single MMA-issuing
     // thread pays a fixed cost per stage, so stages are as large as the work allows:
@@ -72,7 +73,7 @@ extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin
   // A ring stage is always consumed by the same warp (stage s belongs to warp s % warps),
   // which needs stages % warps == 0: a warp then sees every phase of the barriers it waits
   // on.  The ring takes all the shared memory that is left.
-  int warps = (op == FG_OP_W8A16_NK) ? 3 : (p.m_tile == 16 ? 8 : 4);
+  int warps = (op == FG_OP_W8A16_NK) ? 3 : (op == FG_OP_W4A16_NK) ? (p.m_tile == 16 ? 3 : 4) : (p.m_tile == 16 ? 8 : 4);
   const int stage_bytes = chunks * fg_chunk_bytes(op, p.m_tile);
   int stages = 0;
   for (; warps >= 1; --warps) {
@@ -94,7 +95,8 @@ extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin
 extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin_bytes) {
   if (p == nullptr) return FG_ERR_NULL;
   if (smem_optin_bytes <= 0) smem_optin_bytes = 232448;
-  if (p->op < FG_OP_F16_KN || p->op > FG_OP_W8A16_NK) return FG_ERR_PLAN;
+  if (p->op < FG_OP_F16_KN || p->op > FG_OP_W4A16_NK) return FG_ERR_PLAN;
+  const bool quantized = (p->op == FG_OP_W8A16_NK || p->op == FG_OP_W4A16_NK);
   if (p->m_tile != 8 && p->m_tile != 16) return FG_ERR_PLAN;
   if (p->math != 0 && p->math != 2) return FG_ERR_PLAN;
   const int chunk_k = fg_chunk_k(p->op);
@@ -104,10 +106,11 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (p->stages < 2 || p->stages > FG_MAX_STAGES) return FG_ERR_PLAN;
   if (p->math == 2) {
     // tcgen05 variant: fp16 weights, 16-row accumulator in tensor memory, fixed warp roles
-    if (p->op == FG_OP_W8A16_NK || p->m_tile != 16) return FG_ERR_PLAN;
+    if (quantized || p->m_tile != 16) return FG_ERR_PLAN;
   } else {
     if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
-    if (p->op == FG_OP_W8A16_NK && p->consumer_warps > 4) return FG_ERR_PLAN;  // the int8 kernel is built for <= 4
+    // the dequantising kernels are built for <= 4 consumer warps (<= 3 with a 16-row tile)
+    if (quantized && p->consumer_warps > (p->m_tile == 16 ? 3 : 4)) return FG_ERR_PLAN;
     // each stage must always meet the same consumer warp (see fg_plan)
     if (p->stages % p->consumer_warps) return FG_ERR_PLAN;
   }

@@ -165,4 +165,25 @@ __device__ __forceinline__ void dequant_s8x4(uint32_t w, uint32_t& lo, uint32_t&
   asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h), "r"(bias));
 }
 
+// Eight unsigned 4-bit weights of one 32-bit word (nibble i = element i) to four half2, minus the
+// zero point: nibbles (0,4), (1,5), (2,6), (3,7).  A nibble placed under the exponent pattern
+// 0x6400 is the half 1024 + nibble; `magic` is half2(1024 + zero_point), so one subtraction
+// leaves nibble - zero_point exactly (integers well inside the half's 11 significand bits).
+__device__ __forceinline__ void dequant_u4x8(uint32_t w, uint32_t magic, uint32_t (&out)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t v;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(v) : "r"(w >> (4 * i)), "r"(0x000F000Fu), "r"(0x64006400u));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(out[i]) : "r"(v), "r"(magic));
+  }
+}
+__device__ __forceinline__ void lds_v4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+  return d;
+}
+
 }  // namespace fg

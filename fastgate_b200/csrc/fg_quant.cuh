@@ -65,4 +65,56 @@ __global__ void __launch_bounds__(kQuantThreads) fg_quantize_rows_kernel(const _
   }
 }
 
+// ---- int4 -------------------------------------------------------------------------------------
+// Producer of the (W4, scales) pair of fg_gemm_w4a16_nk: unsigned 4-bit values with zero point 8,
+// two per byte (low nibble = even k, the packing of uint4_2 in backend/cuda/hk/utility.cuh:13-36),
+// one fp16 scale per `seg` consecutive k of a row (seg = 128: group-wise; seg = K: per channel):
+//
+//   scale = fp16( max |w| / 7 )                  (1 if the segment is all zero)
+//   q     = clamp( rint( w / float(scale) ) + 8, 0, 15 )
+//
+// One warp per segment: each lane strides over the segment in 8-element vectors.
+__global__ void __launch_bounds__(kQuantThreads) fg_quantize_rows_w4_kernel(const __half* __restrict__ W,
+                                                                            uint8_t* __restrict__ W4,
+                                                                            __half* __restrict__ scales, int K,
+                                                                            int seg, long long segments) {
+  const long long sidx = static_cast<long long>(blockIdx.x) * (kQuantThreads / 32) + (threadIdx.x >> 5);
+  if (sidx >= segments) return;
+  const int lane = threadIdx.x & 31;
+  const int per_row = K / seg;
+  const long long row = sidx / per_row;
+  const int k0 = static_cast<int>(sidx - row * per_row) * seg;
+  const uint4* src = reinterpret_cast<const uint4*>(W + row * K + k0);
+  const int nvec = seg >> 3;
+  uint32_t amax_bits = 0;
+  for (int v = lane; v < nvec; v += 32) {
+    const uint4 q = __ldg(src + v);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) amax_bits = max(amax_bits, max(w[i] & 0x7fffu, (w[i] >> 16) & 0x7fffu));
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, off));
+  const float amax = __half2float(__ushort_as_half(static_cast<unsigned short>(amax_bits)));
+  const __half scale_h = (amax > 0.f) ? __float2half_rn(__fdiv_rn(amax, 7.f)) : __float2half_rn(1.f);
+  const float scale = __half2float(scale_h);
+  if (lane == 0) scales[sidx] = scale_h;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(W4 + (row * K + k0) / 2);
+  for (int v = lane; v < nvec; v += 32) {
+    const uint4 q = __ldg(src + v);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t out = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h2 = *reinterpret_cast<const __half2*>(&w[i]);
+      int a = __float2int_rn(__fdiv_rn(__low2float(h2), scale)) + 8;
+      int b = __float2int_rn(__fdiv_rn(__high2float(h2), scale)) + 8;
+      a = min(15, max(0, a));
+      b = min(15, max(0, b));
+      out |= (static_cast<uint32_t>(a) | (static_cast<uint32_t>(b) << 4)) << (8 * i);
+    }
+    dst[v] = out;
+  }
+}
+
 }  // namespace fg

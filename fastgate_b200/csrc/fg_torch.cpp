@@ -118,6 +118,42 @@ void op_wfirst_int8(at::Tensor W8, at::Tensor x, at::Tensor C, c10::optional<at:
   linear(FG_OP_W8A16_NK, x, W8, C, scales);
 }
 
+// (W4[N,K/2] uint8, x[M,K], C)  int4 weight-only: two unsigned 4-bit values per byte, low nibble
+// first (uint4_2, backend/cuda/hk/utility.cuh:13-36); scales [N] / [N,1] or [N,K/128] or None.
+void op_wfirst_int4(at::Tensor W4, at::Tensor x, at::Tensor C, c10::optional<at::Tensor> scales, int zero_point) {
+  check_tensor(x, "activation", at::kHalf);
+  check_tensor(W4, "weight", at::kByte);
+  check_tensor(C, "output", at::kHalf);
+  if (x.dim() != 2 || W4.dim() != 2) throw std::runtime_error("fastgate_b200: activation and weight must be 2-D");
+  const int64_t M = x.size(0), K = x.size(1), N = W4.size(0);
+  if (W4.size(1) * 2 != K) throw std::runtime_error("fastgate_b200: activation and weight disagree on K");
+  if (C.numel() != M * N) throw std::runtime_error("fastgate_b200: output must hold M*N elements");
+  if (W4.get_device() != x.get_device() || C.get_device() != x.get_device())
+    throw std::runtime_error("fastgate_b200: all tensors must live on one device");
+  if (zero_point < 0 || zero_point > 15) throw std::invalid_argument("fastgate_b200: zero_point must be 0..15");
+  const void* sp = nullptr;
+  int groups = 1;
+  if (scales.has_value() && scales->defined()) {
+    check_tensor(*scales, "scales", at::kHalf);
+    if (N > 0 && scales->numel() % N == 0) groups = static_cast<int>(scales->numel() / N);
+    if (scales->numel() != N * groups || (groups != 1 && groups != K / 128))
+      throw std::runtime_error("fastgate_b200: scales must hold N or N * K/128 elements");
+    sp = scales->data_ptr();
+  }
+  if (M == 0) return;
+  if ((N % 128) != 0 || (K % 128) != 0 || N <= 0 || K <= 0) raise(FG_ERR_SHAPE, true);
+  const c10::cuda::CUDAGuard guard(x.device());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
+  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  int st;
+  {
+    pybind11::gil_scoped_release nogil;
+    st = fg_gemm_w4a16_nk(x.data_ptr(), static_cast<const uint8_t*>(W4.data_ptr()), sp, groups, zero_point,
+                          C.data_ptr(), M, N, K, ws.buf.data_ptr(), ws.bytes, reinterpret_cast<fg_stream_t>(stream));
+  }
+  if (st != FG_OK) raise(st, true);
+}
+
 // ---- N-sharded layer with the all-gather fused into the epilogue --------------------------
 // x[M,K] fp16 (replicated), W[N_local,K] fp16 (this rank's rows); c_ptrs / flag_ptrs are the
 // device addresses, as mapped into this process, of every rank's full output [M, n_total]
@@ -248,6 +284,24 @@ std::pair<at::Tensor, at::Tensor> quantize_int8(at::Tensor W) {
   return {W8, scales};
 }
 
+// W[N,K] fp16 -> (W4[N,K/2] uint8, scales[N,groups] fp16), zero point 8; group_size 128 or 0 (whole row).
+std::pair<at::Tensor, at::Tensor> quantize_int4(at::Tensor W, int group_size) {
+  check_tensor(W, "weight", at::kHalf);
+  if (W.dim() != 2 || (W.size(1) % 128) != 0) throw std::invalid_argument("fastgate_b200: weight [N,K] with K % 128 == 0 expected");
+  if (group_size != 0 && group_size != 128) throw std::invalid_argument("fastgate_b200: group_size must be 128 or 0 (one scale per row)");
+  const int groups = group_size == 0 ? 1 : static_cast<int>(W.size(1) / 128);
+  const c10::cuda::CUDAGuard guard(W.device());
+  at::Tensor W4 = at::empty({W.size(0), W.size(1) / 2}, W.options().dtype(at::kByte));
+  at::Tensor scales = at::empty({W.size(0), groups}, W.options());
+  if (W.numel() == 0) return {W4, scales};
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(W.get_device()).stream();
+  const int st = fg_quantize_rows_w4(W.data_ptr(), static_cast<uint8_t*>(W4.data_ptr()), scales.data_ptr(), groups,
+                                     static_cast<int>(W.size(0)), static_cast<int>(W.size(1)),
+                                     reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+  return {W4, scales};
+}
+
 // cuBLAS comparators of the reference (backend/cuda/hk/hgemm.cu:29-74, hgemm_tr.cu:30-75):
 // library calls, kept only so that scripts which import them keep working.
 void hgemm(at::Tensor A, at::Tensor B, at::Tensor C) {
@@ -297,6 +351,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("linear_fused", &linear_fused, py::arg("x"), py::arg("W"), py::arg("C"), py::arg("scales") = py::none(),
         py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("act") = "none", py::arg("layout") = "nk",
         "C = act(x . W^T * scales + bias) + residual in one kernel (fp32 until the final rounding)");
+  m.def("fastgemv_int4", &op_wfirst_int4, py::arg("W4"), py::arg("x"), py::arg("C"), py::arg("scales") = py::none(),
+        py::arg("zero_point") = 8,
+        "C[M,N] = sum_g scales[n,g] * sum_k x[m,k] * (w4[n,k] - zero_point): W4 [N,K/2] uint8, low nibble = even k");
+  m.def("quantize_int4", &quantize_int4, py::arg("W"), py::arg("group_size") = 128,
+        "W[N,K] fp16 -> (W4 [N,K/2] uint8, scales [N, K/group_size] fp16), zero point 8, for fastgemv_int4");
   m.def("quantize_int8", &quantize_int8, py::arg("W"),
         "W[N,K] fp16 -> (W8 int8, scales fp16): symmetric, one scale per output channel, for fastgemv_int8");
   m.def("launch_count", []() { return fg_launch_count(); });

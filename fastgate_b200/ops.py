@@ -10,6 +10,9 @@ All write ``C = A.B`` in place (fp32 accumulation, one rounding to fp16) on the 
 CUDA stream and raise ``ValueError`` with the reference's message when K or N is not a
 multiple of 128 (hk/edgemm.cu:107-109).  Ops that took a split-K hint ``bz`` still accept it.
 ``fastgemv_int8`` takes an optional 4th tensor ``scales[N]`` (fp16, one per output channel).
+``fastgemv_int4(W4[N,K/2] uint8, x, C, scales=None, zero_point=8)`` is the int4 weight-only sibling
+(two unsigned 4-bit weights per byte, low nibble first, hk/utility.cuh:13-36; scales [N] or
+[N, K/128]); the reference has the kernel (hk/fastgemv.cuh:394-495) but no operator for it.
 """
 from . import _C
 
@@ -30,7 +33,8 @@ BZ_OPS = (
 )
 COMPARATORS = ("hgemm", "hgemm_tr")
 
-EXTRA = ("linear_nk_push", "push_wait", "workspace_status", "quantize_int8", "linear_fused")
+EXTRA = ("linear_nk_push", "push_wait", "workspace_status", "quantize_int8", "linear_fused", "fastgemv_int4",
+         "quantize_int4")
 
 __all__ = list(KN_OPS + NK_OPS + WF_OPS + COMPARATORS + EXTRA) + ["launch_count", "version",
                                                          "KN_OPS", "NK_OPS", "WF_OPS", "BZ_OPS"]

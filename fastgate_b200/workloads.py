@@ -10,6 +10,8 @@ kernels all see identical bits.  Everything is generated on the CPU with a
   activations  N(0, 1)         -> fp16        seed S + 100000
   int8 weights uniform integers in [-127, 127]
   int8 scales  uniform [0.5, 1.5] / 127 -> fp16   seed S + 200000
+  int4 weights uniform bytes (two nibbles 0..15 each), zero point 8
+  int4 scales  uniform [0.5, 1.5] / 8 -> fp16, [N, groups]   seed S + 200000
 """
 from __future__ import annotations
 
@@ -17,7 +19,7 @@ from dataclasses import dataclass
 
 import torch
 
-OP_KN, OP_NK, OP_W8 = 0, 1, 2  # FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK
+OP_KN, OP_NK, OP_W8, OP_W4 = 0, 1, 2, 3  # FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK, FG_OP_W4A16_NK
 
 
 @dataclass(frozen=True)
@@ -28,9 +30,12 @@ class Case:
     N: int
     K: int
     seed: int
+    groups: int = 1  # int4: scales per weight row (1 or K / 128)
 
     @property
     def weight_bytes(self) -> int:
+        if self.op == OP_W4:
+            return self.N * self.K // 2
         return self.N * self.K * (1 if self.op == OP_W8 else 2)
 
     @property
@@ -39,6 +44,8 @@ class Case:
         b = self.weight_bytes + 2 * self.M * self.K + 2 * self.M * self.N
         if self.op == OP_W8:
             b += 2 * self.N
+        if self.op == OP_W4:
+            b += 2 * self.N * self.groups
         return b
 
 
@@ -47,6 +54,8 @@ def make_weight(case: Case) -> torch.Tensor:
     g = torch.Generator(device="cpu").manual_seed(case.seed)
     if case.op == OP_W8:
         return torch.randint(-127, 128, (case.N, case.K), generator=g, dtype=torch.int8)
+    if case.op == OP_W4:
+        return torch.randint(0, 256, (case.N, case.K // 2), generator=g, dtype=torch.uint8)
     w = (torch.randn(case.N, case.K, generator=g) / case.K ** 0.5).to(torch.float16)
     return w.t().contiguous() if case.op == OP_KN else w
 
@@ -57,9 +66,11 @@ def make_activation(case: Case) -> torch.Tensor:
 
 
 def make_scales(case: Case):
-    if case.op != OP_W8:
+    if case.op not in (OP_W8, OP_W4):
         return None
     g = torch.Generator(device="cpu").manual_seed(case.seed + 200000)
+    if case.op == OP_W4:
+        return ((torch.rand(case.N, case.groups, generator=g) + 0.5) / 8.0).to(torch.float16)
     return ((torch.rand(case.N, generator=g) + 0.5) / 127.0).to(torch.float16)
 
 
@@ -83,6 +94,11 @@ def cfg3() -> list[Case]:
 def cfg4() -> list[Case]:
     """fastgemv_int8 with per-output-channel scales: M in {1,8}, N=28672, K=8192."""
     return [Case(f"fastgemv_int8_M{m}", OP_W8, m, 28672, 8192, 4000 + m) for m in (1, 8)]
+
+
+def w4() -> list[Case]:
+    """fastgemv_int4 with one scale per 128 k: the shape of cfg4 with 4-bit weights, M in {1,8,16}."""
+    return [Case(f"fastgemv_int4_M{m}", OP_W4, m, 28672, 8192, 4100 + m, 8192 // 128) for m in (1, 8, 16)]
 
 
 DIT_LAYERS = 40

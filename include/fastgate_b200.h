@@ -54,7 +54,8 @@ enum {
 enum {
   FG_OP_F16_KN = 0,  /* weight B[K,N] fp16  (edgemm_m8n128k64x4, flat_gemm_*)     */
   FG_OP_F16_NK = 1,  /* weight W[N,K] fp16  (edgemm_*_bt, gemm_*_bt, fastgemv*)   */
-  FG_OP_W8A16_NK = 2 /* weight W8[N,K] int8 + optional fp16 scale per row of W8   */
+  FG_OP_W8A16_NK = 2, /* weight W8[N,K] int8 + optional fp16 scale per row of W8  */
+  FG_OP_W4A16_NK = 3  /* weight W4[N,K/2] bytes, two unsigned 4-bit values each      */
 };
 
 /*
@@ -120,6 +121,23 @@ int fg_gemm_f16_nk(const void* x, const void* W, void* C, int M, int N, int K,
  * C[M,N] fp16 = (x . W8^T) * scales[n]. */
 int fg_gemm_w8a16_nk(const void* x, const int8_t* W8, const void* scales, void* C,
                      int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* int4 weight-only GEMV/GEMM: x[M,K] fp16, W4[N,K/2] bytes, C[M,N] fp16 =
+ *     sum over groups g of scales[n,g] * sum_{k in g} x[m,k] * (w4[n,k] - zero_point).
+ * Byte j of a row holds k = 2j in its low and k = 2j+1 in its high nibble, unsigned 0..15: the
+ * packing of uint4_2 (hk/utility.cuh:13-36) that gemv_quantized_int4 (hk/fastgemv.cuh:394-495)
+ * reads.  That kernel has no host wrapper in the reference and takes ONE scale and zero point
+ * for the whole matrix; here scales is [N, groups] fp16 with groups = 1 (one scale per output
+ * channel) or K/128 (one per 128 consecutive k), or NULL (scale 1), and zero_point an integer
+ * 0..15 (8 = symmetric).  The reference's scalar form is scales filled with one value. */
+int fg_gemm_w4a16_nk(const void* x, const uint8_t* W4, const void* scales, int groups, int zero_point,
+                     void* C, int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* Group-wise asymmetric-range quantiser for fg_gemm_w4a16_nk: W[N,K] fp16 -> W4[N,K/2] and
+ * scales[N,groups] fp16, groups = 1 or K/128; per group scale = fp16(max|W| / 7) (1 for an
+ * all-zero group), q = clamp(rint(W / scale) + 8, 0, 15), zero point 8.  No counterpart in the
+ * reference (it only generates random nibbles, hk/utility.cu generate_random_int4_numbers). */
+int fg_quantize_rows_w4(const void* W, uint8_t* W4, void* scales, int groups, int N, int K, fg_stream_t stream);
 
 /* Same operation as fg_gemm_f16_nk for callers that cannot allocate device memory: a
  * plugin that is handed its buffers and nothing else, code running under a fixed memory

@@ -3,7 +3,8 @@
 The unmodified sources backend/cuda/hk/{edgemm,edgemm_tr,flatgemm,fastgemv}.cu and
 backend/cuda/czn/fastgemm.cu are compiled from the reference checkout where it lies
 (nothing is copied into this repository) and linked with ref_shim.cpp into
-oracle/_ref/fastgate_ref.so, a torch extension.  The reference's own setup.py is not used:
+oracle/_ref/fastgate_ref.so, a torch extension.  ref_int4_launch.cu adds a launcher for
+gemv_quantized_int4, a kernel the reference defines (hk/fastgemv.cuh:394-495) but never launches.  The reference's own setup.py is not used:
 it lists source files that do not exist and defaults to another vendor's backend.
 
 The result serves two purposes, both as a checker / comparator, never as the product:
@@ -54,8 +55,14 @@ def build(reference: str = "/root/reference", force: bool = False) -> str | None
         subprocess.run([*nvcc, os.path.join(cuda_dir, rel), "-o", obj], check=True)
         return obj
 
-    with ThreadPoolExecutor(max_workers=5) as ex:
-        objs = list(ex.map(compile_one, SOURCES))
+    def compile_launcher() -> str:  # our launcher around the reference's int4 kernel (no launcher upstream)
+        obj = os.path.join(OUT, "ref_int4_launch.o")
+        subprocess.run([*nvcc, os.path.join(HERE, "ref_int4_launch.cu"), "-o", obj], check=True)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=6) as ex:
+        launcher = ex.submit(compile_launcher)
+        objs = list(ex.map(compile_one, SOURCES)) + [launcher.result()]
     shim_obj = os.path.join(OUT, "ref_shim.o")
     subprocess.run(["g++", "-fPIC", "-w", *common, *inc, "-c", os.path.join(HERE, "ref_shim.cpp"), "-o", shim_obj],
                    check=True)

@@ -18,13 +18,16 @@
  *        fgo_gemm_fp16_ref      gemm_fp16 (extend)     backend/cuda/hk/fastgemv.cuh:244-311
  *        fgo_gemv_int8_ref      gemv_quantized_int8    backend/cuda/hk/fastgemv.cuh:316-389
  *                               (scale 1, zero-point 0 as launched, hk/fastgemv.cu:50-59)
+ *        fgo_gemv_int4_ref      gemv_quantized_int4    backend/cuda/hk/fastgemv.cuh:394-495
+ *                               (no launcher in the reference: the int8 one's 128x4 shape)
  *
  *  (2) the "fp32-accumulated reference" the tolerance max|d| <= 1e-2*max(1,|ref|) is
  *      stated against, for all three operand layouts; the tensor-core kernels of the
  *      reference (eed_hgemm_m8n128k64x4_v7/_v7_bt, backend/cuda/hk/edgemm.cuh:1669-1868,
  *      1467-1667) accumulate in fp16 inside wmma in a hardware-defined order that cannot
  *      be restated bit-exactly, so for them this is the oracle:
- *        fgo_gemm_nk / fgo_gemm_kn / fgo_gemm_w8a16_nk   (double accumulation, fp32 out)
+ *        fgo_gemm_nk / fgo_gemm_kn / fgo_gemm_w8a16_nk / fgo_gemm_w4a16_nk
+ *                                                         (double accumulation, fp32 out)
  *        fgo_gemm_nk_f32seq                               (sequential fp32 accumulation)
  *
  *  plus fgo_ref_splitk_bt, the reference's split-K choice (backend/cuda/hk/edgemm.cu:287-305).
@@ -176,6 +179,41 @@ void fgo_gemv_int8_ref(const int8_t* W8, const uint16_t* x, uint16_t* y, int N, 
   }
 }
 
+/* y[n] = sum over threads of scale * sum_k x[k] * (float(nibble[n,k]) - zero_point):
+ * gemv_quantized_int4 (hk/fastgemv.cuh:394-495).  W4 is [N, K/2] bytes, low nibble = even k
+ * (uint4_2, hk/utility.cuh:13-36).  Thread tid of a 128-thread row takes 16 consecutive k at
+ * 16 * (tid + 128 * iter) (:409-412, two float4 of activations against two uint4_2_4), adds the
+ * sixteen products in k order (:437-468), scales its own sum (:472) and the block reduces as
+ * in the other GEMV kernels (:474-494).  With an integer zero point every product is exact in
+ * fp32, so contraction to FMA cannot change the result.  The reference has no launcher for
+ * this kernel; the shape of its int8 launcher (128 x 4 threads, num_per_thread = K / 128,
+ * hk/fastgemv.cu:39-59) is assumed. */
+void fgo_gemv_int4_ref(const uint8_t* W4, const uint16_t* x, uint16_t* y, int N, int K, float scale,
+                       float zero_point) {
+  const int n8 = K >> 3;
+  const int iters = ((K / 128) + 15) / 16;
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    float ts[128];
+    const uint8_t* wrow = W4 + (size_t)n * (K / 2);
+    for (int tid = 0; tid < 128; ++tid) {
+      float sum = 0.f;
+      for (int it = 0; it < iters; ++it) {
+        const int j = 2 * (tid + it * 128);
+        if (j < n8)
+          for (int e = 0; e < 16; ++e) {
+            const int k = 8 * j + e;
+            const uint8_t byte = wrow[k >> 1];
+            const float w = (float)((k & 1) ? (byte >> 4) & 0x0F : byte & 0x0F);
+            sum += h2f(x[k]) * (w - zero_point);
+          }
+      }
+      ts[tid] = sum * scale;
+    }
+    y[n] = f2h(block_reduce_ref(ts));
+  }
+}
+
 /* ---- fp32-accumulated reference ("the oracle" for the tolerance) ---------------------- */
 
 /* C32[m,n] = sum_k x[m,k]*W[n,k], double accumulation, rounded once to fp32. */
@@ -241,6 +279,30 @@ void fgo_gemm_w8a16_nk(const uint16_t* x, const int8_t* W8, const uint16_t* scal
   }
 }
 
+/* C32[m,n] = sum_g scales[n,g] * sum_{k in group g} x[m,k] * (nibble[n,k] - zero_point); groups
+ * scales per row (1, or K/128 for one per 128 consecutive k); scales NULL = 1.  Double accumulation. */
+void fgo_gemm_w4a16_nk(const uint16_t* x, const uint8_t* W4, const uint16_t* scales, int groups, int zero_point,
+                       float* C32, int M, int N, int K) {
+  const int seg = K / groups;
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    const uint8_t* w = W4 + (size_t)n * (K / 2);
+    for (int m = 0; m < M; ++m) {
+      const uint16_t* xr = x + (size_t)m * K;
+      double total = 0.0;
+      for (int g = 0; g < groups; ++g) {
+        double acc = 0.0;
+        for (int k = g * seg; k < (g + 1) * seg; ++k) {
+          const int q = (k & 1) ? (w[k >> 1] >> 4) & 0x0F : w[k >> 1] & 0x0F;
+          acc += (double)h2f(xr[k]) * (double)(q - zero_point);
+        }
+        total += acc * (double)(scales ? h2f(scales[(size_t)n * groups + g]) : 1.0f);
+      }
+      C32[(size_t)m * N + n] = (float)total;
+    }
+  }
+}
+
 /* fp32 -> fp16 rounding of a whole array (round to nearest even). */
 void fgo_round_to_f16(const float* src, uint16_t* dst, size_t n) {
   for (size_t i = 0; i < n; ++i) dst[i] = f2h(src[i]);
@@ -287,6 +349,38 @@ void fgo_quantize_rows_w8(const uint16_t* W, int8_t* W8, uint16_t* scales, int N
       if (q > 127.f) q = 127.f;
       if (q < -127.f) q = -127.f;
       W8[(size_t)n * K + k] = (int8_t)q;
+    }
+  }
+}
+
+/* Group-wise int4 quantiser (no counterpart in the reference): per segment of K/groups values
+ * scale = fp16(max|w| / 7) (1 if all zero), q = clamp(rint(w / scale) + 8, 0, 15), packed two
+ * per byte with the even k in the low nibble. */
+void fgo_quantize_rows_w4(const uint16_t* W, uint8_t* W4, uint16_t* scales, int groups, int N, int K) {
+  const int seg = K / groups;
+#pragma omp parallel for schedule(static)
+  for (int n = 0; n < N; ++n) {
+    const uint16_t* w = W + (size_t)n * K;
+    uint8_t* out = W4 + (size_t)n * (K / 2);
+    for (int g = 0; g < groups; ++g) {
+      float amax = 0.f;
+      for (int k = g * seg; k < (g + 1) * seg; ++k) {
+        const float a = fabsf(h2f(w[k]));
+        if (a > amax) amax = a;
+      }
+      const uint16_t sh = amax > 0.f ? f2h(amax / 7.f) : f2h(1.f);
+      const float s = h2f(sh);
+      scales[(size_t)n * groups + g] = sh;
+      for (int k = g * seg; k < (g + 1) * seg; k += 2) {
+        int q[2];
+        for (int e = 0; e < 2; ++e) {
+          float v = nearbyintf(h2f(w[k + e]) / s) + 8.f;
+          if (v > 15.f) v = 15.f;
+          if (v < 0.f) v = 0.f;
+          q[e] = (int)v;
+        }
+        out[k >> 1] = (uint8_t)(q[0] | (q[1] << 4));
+      }
     }
   }
 }

@@ -95,6 +95,19 @@ def gemv_int8_ref(W8, x, scale: float = 1.0, zero_point: float = 0.0) -> np.ndar
     return y
 
 
+def gemv_int4_ref(W4, x, scale: float = 1.0, zero_point: float = 8.0) -> np.ndarray:
+    """gemv_quantized_int4 of the reference, launched 128 x 4 like its int8 sibling: y[N] fp16.
+    W4 is [N, K/2] uint8, low nibble = even k."""
+    W4 = np.ascontiguousarray(W4)
+    assert W4.dtype == np.uint8
+    x = _h(x).reshape(-1)
+    N, K = W4.shape[0], W4.shape[1] * 2
+    assert x.shape[0] == K
+    y = np.empty(N, np.float16)
+    lib().fgo_gemv_int4_ref(_p(W4), _p(x), _p(y), N, K, ctypes.c_float(scale), ctypes.c_float(zero_point))
+    return y
+
+
 # ---- fp32-accumulated reference ----------------------------------------------------------
 def gemm_nk(x, W) -> np.ndarray:
     """C32[M,N] = x[M,K] . W[N,K]^T (double accumulation, fp32 result)."""
@@ -152,6 +165,36 @@ def epilogue(C32, bias=None, residual=None, act: int = 0) -> np.ndarray:
     r = _p(_h(residual).reshape(M, N)) if residual is not None else None
     lib().fgo_epilogue(_p(out), b, r, int(act), M, N)
     return out
+
+
+def gemm_w4a16_nk(x, W4, scales=None, zero_point: int = 8) -> np.ndarray:
+    """C32[M,N] = sum_g scales[n,g] * sum_{k in g} x[m,k] * (nibble[n,k] - zero_point); scales is
+    [N] / [N,1] (per channel), [N, K/128] (group-wise) or None (1)."""
+    x = _h(x)
+    W4 = np.ascontiguousarray(W4)
+    assert W4.dtype == np.uint8
+    M, K = x.shape
+    N = W4.shape[0]
+    assert W4.shape[1] * 2 == K
+    C = np.empty((M, N), np.float32)
+    sp, groups = None, 1
+    if scales is not None:
+        scales = _h(scales).reshape(N, -1)
+        groups = scales.shape[1]
+        assert groups in (1, K // 128)
+        sp = _p(scales)
+    lib().fgo_gemm_w4a16_nk(_p(x), _p(W4), sp, groups, int(zero_point), _p(C), M, N, K)
+    return C
+
+
+def quantize_rows_w4(W, groups: int = 1):
+    """W[N,K] fp16 -> (W4 [N,K/2] uint8, scales [N,groups] fp16), zero point 8."""
+    W = _h(W)
+    N, K = W.shape
+    W4 = np.empty((N, K // 2), np.uint8)
+    scales = np.empty((N, groups), np.float16)
+    lib().fgo_quantize_rows_w4(_p(W), _p(W4), _p(scales), groups, N, K)
+    return W4, scales
 
 
 def quantize_rows_w8(W):

@@ -12,7 +12,19 @@
 #include "hk/fastgemv.h"    // backend/cuda/hk/fastgemv.h:4-7
 #include "czn/fastgemm.h"   // backend/cuda/czn/fastgemm.h:4
 
+// launcher of ref_int4_launch.cu around the reference's gemv_quantized_int4 (hk/fastgemv.cuh:394-495)
+extern "C" int fastgate_ref_gemv_int4(const void* W4, const void* x, void* y, int N, int K, float scale,
+                                      float zero_point, void* stream);
+static void gemv_int4(at::Tensor W4, at::Tensor x, at::Tensor y, double scale, double zero_point) {
+  const int N = static_cast<int>(W4.size(0)), K = static_cast<int>(W4.size(1)) * 2;
+  TORCH_CHECK(W4.is_cuda() && x.is_cuda() && y.is_cuda() && N % 4 == 0 && K % 128 == 0 && x.numel() == K && y.numel() == N);
+  const int err = fastgate_ref_gemv_int4(W4.data_ptr(), x.data_ptr(), y.data_ptr(), N, K, static_cast<float>(scale),
+                                         static_cast<float>(zero_point), nullptr);
+  TORCH_CHECK(err == 0, "gemv_quantized_int4 launch failed: ", err);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemv_int4", &gemv_int4);
   m.def("edgemm", &edgemm);
   m.def("edgemm_m8n256k64", &edgemm_m8n256k64);
   m.def("edgemm_m8n128k64", &edgemm_m8n128k64);

@@ -58,3 +58,37 @@ def test_fp32_oracle_within_tolerance_of_reference(key):
     else:
         ref = o.gemm_nk(x, W)
     o.check_tolerance(gold, ref, key)
+
+
+# ---- int4: gemv_quantized_int4 (hk/fastgemv.cuh:394-495) -------------------------------------------
+# reference_b200_int4.npz: outputs of the reference's kernel on a B200, launched by
+# oracle/ref_int4_launch.cu (the reference has no launcher for it), one scale and zero point
+# for the whole matrix.
+GOLD4 = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_b200_int4.npz"))
+KEYS4 = sorted(k for k in GOLD4.files if "__" not in k)
+
+
+def _case4(key):
+    op, M, N, K, seed, zp = (int(v) for v in GOLD4[key + "__meta"])
+    case = wl.Case(key, op, M, N, K, seed)
+    scale = float(GOLD4[key + "__scale"][0])
+    return wl.make_activation(case).numpy(), wl.make_weight(case).numpy(), scale, zp, GOLD4[key].view(np.float16)
+
+
+def test_int4_fixture_inventory():
+    assert len(KEYS4) == 3 and any(k.endswith("zp5") for k in KEYS4)
+
+
+@pytest.mark.parametrize("key", KEYS4)
+def test_int4_restatement_matches_reference_bits(key):
+    x, W4, scale, zp, gold = _case4(key)
+    mine = o.gemv_int4_ref(W4, x, scale, float(zp))
+    assert np.array_equal(mine.view(np.uint16), gold.view(np.uint16)), key
+
+
+@pytest.mark.parametrize("key", KEYS4)
+def test_int4_fp32_oracle_within_tolerance_of_reference(key):
+    x, W4, scale, zp, gold = _case4(key)
+    N = W4.shape[0]
+    ref = o.gemm_w4a16_nk(x, W4, np.full(N, scale, np.float16), zp)
+    o.check_tolerance(gold[None], ref, key)

@@ -122,3 +122,51 @@ def test_quantiser_restatement():
     # independent numpy restatement
     sf = s.astype(np.float32)[:, None]
     assert np.array_equal(q, np.clip(np.rint(W.astype(np.float32) / sf), -127, 127).astype(np.int8))
+
+
+def _unpack_w4(W4):
+    q = np.empty((W4.shape[0], W4.shape[1] * 2), np.int32)
+    q[:, 0::2] = W4 & 0x0F   # even k in the low nibble (uint4_2::getX, hk/utility.cuh:22-24)
+    q[:, 1::2] = W4 >> 4     # odd k in the high nibble (getY, :26-28)
+    return q
+
+
+def test_int4_reference_semantics():
+    rng = np.random.default_rng(8)
+    N, K = 128, 2048
+    W4 = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
+    x = rng.standard_normal((2, K)).astype(np.float16)
+    q = _unpack_w4(W4).astype(np.float64)
+    for zp in (0, 8, 11):
+        exact = x.astype(np.float64) @ (q - zp).T
+        assert np.allclose(o.gemm_w4a16_nk(x, W4, None, zp), exact, rtol=1e-6, atol=1e-3)
+    # one scale per channel, one scale per 128 k
+    s1 = (rng.uniform(0.5, 1.5, N) / 8).astype(np.float16)
+    assert np.allclose(o.gemm_w4a16_nk(x, W4, s1, 8), (x.astype(np.float64) @ (q - 8).T) * s1.astype(np.float64),
+                       rtol=1e-6, atol=1e-4)
+    sg = (rng.uniform(0.5, 1.5, (N, K // 128)) / 8).astype(np.float16)
+    wdq = (q - 8) * np.repeat(sg.astype(np.float64), 128, axis=1)
+    assert np.allclose(o.gemm_w4a16_nk(x, W4, sg, 8), x.astype(np.float64) @ wdq.T, rtol=1e-6, atol=1e-4)
+    # the reference's kernel (scalar scale and zero point) sits within the tolerance of that reference
+    y = o.gemv_int4_ref(W4, x[0], 0.0625, 8.0)
+    o.check_tolerance(y[None], o.gemm_w4a16_nk(x[:1], W4, np.full(N, 0.0625, np.float16), 8), "gemv_quantized_int4")
+    # all-ones known answer: every output is K * (15 - zero_point) * scale
+    ones = np.ones(K, np.float16)
+    y1 = o.gemv_int4_ref(np.full((N, K // 2), 0xFF, np.uint8), ones, 0.03125, 8.0)
+    assert np.array_equal(y1, np.full(N, K * 7 * 0.03125, np.float16))
+
+
+def test_int4_quantiser_restatement():
+    rng = np.random.default_rng(4)
+    W = (rng.standard_normal((16, 512)) / 20).astype(np.float16)
+    W[3] = 0
+    for groups in (1, 4):
+        q4, s = o.quantize_rows_w4(W, groups)
+        assert q4.shape == (16, 256) and s.shape == (16, groups)
+        q = _unpack_w4(q4)
+        assert (q[3] == 8).all() and (s[3] == 1.0).all()
+        sf = np.repeat(s.astype(np.float32), 512 // groups, axis=1)
+        assert np.array_equal(q, np.clip(np.rint(W.astype(np.float32) / sf) + 8, 0, 15).astype(np.int32))
+        err = np.abs((q - 8) * sf - W.astype(np.float32))
+        assert (err <= 0.51 * sf + 1e-6).all()
+        assert q.max() == 15 and q.min() >= 1  # the maximum maps to +7, nothing below -7

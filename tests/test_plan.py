@@ -10,7 +10,7 @@ import pytest
 from fastgate_b200 import capi
 
 B200 = dict(sm_count=148, smem_optin=232448)
-CHUNK_K = {0: 64, 1: 64, 2: 128}
+CHUNK_K = {0: 64, 1: 64, 2: 128, 3: 256}
 
 
 def _range_begin(c, total, grid):
@@ -60,7 +60,8 @@ def simulate(tiles, k_blocks, grid):
 SHAPES = [(1, 16, 8192, 8192), (1, 1, 11008, 4096), (1, 1, 4096, 11008), (0, 8, 4096, 4096),
           (2, 1, 28672, 8192), (2, 8, 28672, 8192), (1, 16, 9216, 3072), (1, 16, 3072, 3072),
           (1, 16, 12288, 3072), (1, 16, 3072, 12288), (1, 4, 128, 128), (0, 3, 256, 384),
-          (1, 16, 1152, 3072), (1, 16, 384, 3072), (1, 16, 1536, 3072), (1, 33, 4096, 4096)]
+          (1, 16, 1152, 3072), (1, 16, 384, 3072), (1, 16, 1536, 3072), (1, 33, 4096, 4096),
+          (3, 1, 28672, 8192), (3, 16, 28672, 8192), (3, 8, 256, 384), (2, 16, 4096, 4096)]
 
 
 @pytest.mark.parametrize("op,M,N,K", SHAPES)
@@ -74,11 +75,11 @@ def test_plan_invariants(op, M, N, K):
     assert p.stages >= 2
     if p.math == 0:
         assert p.stages % p.consumer_warps == 0, "a ring slot must always meet the same warp"
-        if op == 2:
-            assert p.consumer_warps <= 4
+        if op in (2, 3):  # the dequantising kernels: <= 384 threads per CTA
+            assert p.consumer_warps <= (3 if p.m_tile == 16 else 4)
     else:
-        assert p.math == 2 and op != 2 and p.m_tile == 16, "tcgen05 kernel: fp16 weights, 16-row accumulator"
-    assert (p.math == 2) == (op != 2 and M > 8), "more than 8 rows of fp16 go to the tcgen05 kernel"
+        assert p.math == 2 and op in (0, 1) and p.m_tile == 16, "tcgen05 kernel: fp16 weights, 16-row accumulator"
+    assert (p.math == 2) == (op in (0, 1) and M > 8), "more than 8 rows of fp16 go to the tcgen05 kernel"
     assert p.smem_bytes <= 232448
     assert p.passes == -(-M // 16)
     assert capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK
