@@ -16,6 +16,7 @@
 #include "fg_umma.cuh"
 #include "fg_umma_group.cuh"
 #include "fg_umma_chain.cuh"
+#include "fg_umma_q.cuh"
 #include "fg_quant.cuh"
 #include "fg_layout.h"
 
@@ -65,7 +66,7 @@ struct DeviceInfo {
   int smem_optin = 0;
   int cc_major = 0;
   int smem_set[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
-  int smem_set_umma[3] = {0, 0, 0};
+  int smem_set_umma[4] = {0, 0, 0, 0};
   int smem_set_group[2] = {0, 0};
   int smem_set_chain[2] = {0, 0};
 };
@@ -147,6 +148,8 @@ KernelFn pick_kernel(int op, int m_tile) {
 }
 
 KernelFn pick_umma_kernel(int op) {
+  if (op == FG_OP_W8A16_NK) return fg::fg_umma_q_kernel<fg::kOpW8A16NK>;
+  if (op == FG_OP_W4A16_NK) return fg::fg_umma_q_kernel<fg::kOpW4A16NK>;
   return op == FG_OP_F16_KN ? fg::fg_umma_kernel<fg::kOpF16KN> : fg::fg_umma_kernel<fg::kOpF16NK>;
 }
 
@@ -188,7 +191,9 @@ int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const
   cfg.gridDim = dim3(pl.grid);
   // tcgen05 kernel: fixed warp roles; mma.sync kernel: consumers + one copy-issuing warp +
   // m_tile/4 warps that finish split tiles
-  cfg.blockDim = dim3(pl.math == 2 ? fg::kUmmaThreads : (pl.consumer_warps + 1 + 2 * (pl.m_tile / 4)) * 32);
+  const bool quantized = (pl.op == FG_OP_W8A16_NK || pl.op == FG_OP_W4A16_NK);
+  cfg.blockDim = dim3(pl.math == 2 ? (quantized ? fg::kUmmaQThreads : fg::kUmmaThreads)
+                                   : (pl.consumer_warps + 1 + 2 * (pl.m_tile / 4)) * 32);
   cfg.dynamicSmemBytes = pl.smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -413,7 +418,8 @@ int fg_gemm_w4a16_nk(const void* x, const uint8_t* W4, const void* scales, int g
     DeviceInfo* dev = nullptr;
     if ((st = device_info(&dev)) != FG_OK) return st;
     fg_plan_t pl;
-    if ((st = fg_plan(FG_OP_W4A16_NK, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+    // one fp32 scaling per 128-k group: the mma.sync kernel (the tcgen05 one scales per channel only)
+    if ((st = fg_plan_mma_sync(FG_OP_W4A16_NK, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
     return run_planned(pl, dev, x, W4, scales, C, M, N, K, ws, reinterpret_cast<cudaStream_t>(stream), nullptr,
                        nullptr, &qa);
   }

@@ -11,8 +11,22 @@
 #include "../../include/fastgate_b200.h"
 #include "fg_layout.h"
 
+static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_bytes, fg_plan_t* out,
+                     bool force_mma_sync);
+
 extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
                        fg_plan_t* out) {
+  return plan_impl(op, M, N, K, sm_count, smem_optin_bytes, out, false);
+}
+
+// Internal (fg_layout.h): the plan of the mma.sync kernel for a quantized op whatever M is.
+extern "C" int fg_plan_mma_sync(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
+                                fg_plan_t* out) {
+  return plan_impl(op, M, N, K, sm_count, smem_optin_bytes, out, true);
+}
+
+static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_bytes, fg_plan_t* out,
+                     bool force_mma_sync) {
   if (out == nullptr) return FG_ERR_NULL;
   std::memset(out, 0, sizeof(*out));
   if (op < FG_OP_F16_KN || op > FG_OP_W4A16_NK) return FG_ERR_PLAN;
@@ -55,6 +69,29 @@ extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin
     if (p.stages < 2) return FG_ERR_PLAN;
     p.pdl = 1;
     p.smem_bytes = fg_umma_smem_bytes(op, chunks, p.stages);
+    *out = p;
+    return FG_OK;
+  }
+  if (quantized && p.m_tile == 16 && !force_mma_sync) {
+    // Quantized weights, more than 8 token rows: warps dequantise landed stages into fp16 staging
+    // tiles for tcgen05.mma (fg_umma_q_kernel).  Measured on B200 at 28672 x 8192, M = 16: int8
+    // 66 us against 70 us for the 16-row mma.sync kernel, int4 58 us against 86 us.  Up to 8 rows
+    // the mma.sync kernel is as fast or faster (int8 follows HBM there).  Group-wise int4 scales
+    // need fp32 scaling per group, which only the mma.sync kernel does: its caller asks for it.
+    p.math = 2;
+    p.m_tile = 16;
+    p.consumer_warps = 4;
+    const int chunks = 1;  // 16 KB of packed weights per stage: the ring is short (64 KB go to staging)
+    p.k_per_stage = chunks * chunk_k;
+    p.k_blocks = (K + p.k_per_stage - 1) / p.k_per_stage;
+    const long long units = static_cast<long long>(p.tiles) * p.k_blocks;
+    p.grid = static_cast<int>(std::min<long long>(std::min(sm_count, FG_MAX_GRID), units));
+    if (units * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;
+    const int stage_bytes = chunks * fg_chunk_bytes(op, 16);
+    p.stages = std::min((smem_optin_bytes - 1024 - 96 - FG_UMMA_Q_STAGING_BYTES) / (stage_bytes + 16), FG_MAX_STAGES);
+    if (p.stages < 2) return FG_ERR_PLAN;
+    p.pdl = 1;
+    p.smem_bytes = fg_umma_q_smem_bytes(op, chunks, p.stages);
     *out = p;
     return FG_OK;
   }
@@ -105,8 +142,9 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (chunks < 1 || chunks > 4) return FG_ERR_PLAN;
   if (p->stages < 2 || p->stages > FG_MAX_STAGES) return FG_ERR_PLAN;
   if (p->math == 2) {
-    // tcgen05 variant: fp16 weights, 16-row accumulator in tensor memory, fixed warp roles
-    if (quantized || p->m_tile != 16) return FG_ERR_PLAN;
+    // tcgen05 variants: 16-row accumulator in tensor memory, fixed warp roles
+    if (p->m_tile != 16) return FG_ERR_PLAN;
+    if (quantized && chunks > 4) return FG_ERR_PLAN;
   } else {
     if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
     // the dequantising kernels are built for <= 4 consumer warps (<= 3 with a 16-row tile)
@@ -119,7 +157,8 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   const long long units = static_cast<long long>(p->tiles) * p->k_blocks;
   if (p->grid < 1 || p->grid > FG_MAX_GRID || p->grid > units) return FG_ERR_PLAN;
   if (units * p->grid >= (1LL << 31)) return FG_ERR_PLAN;  // the kernel's index math is 32-bit
-  const int want_smem = (p->math == 2) ? fg_umma_smem_bytes(p->op, chunks, p->stages)
+  const int want_smem = (p->math == 2) ? (quantized ? fg_umma_q_smem_bytes(p->op, chunks, p->stages)
+                                                    : fg_umma_smem_bytes(p->op, chunks, p->stages))
                                        : fg_smem_bytes(p->op, p->m_tile, chunks, p->stages, p->consumer_warps);
   if (p->smem_bytes != want_smem) return FG_ERR_PLAN;
   if (p->smem_bytes > smem_optin_bytes) return FG_ERR_PLAN;

@@ -87,6 +87,8 @@ __host__ __device__ constexpr uint32_t umma_idesc(bool a_mn_major) {
 // One output element of row m, column n (scale, round, store; push-aware like store_out2).
 template <int OP, int ACT>
 __device__ __forceinline__ void store_out1(const KParams& p, int m, int n, float v) {
+  if ((OP == kOpW8A16NK || (OP == kOpW4A16NK && p.scale_groups <= 1)) && p.scales != nullptr)
+    v *= __half2float(p.scales[n]);  // one scale per output channel, applied in fp32
   if (ACT != kActNone || p.bias != nullptr || p.residual != nullptr) v = epilogue1<ACT>(p, m, n, v);
   const __half h = __float2half_rn(v);
   if (p.world == 0) {

@@ -1,0 +1,361 @@
+// tcgen05 kernel for the quantized ops (int8 and packed int4 weights, fp16 activations).
+//
+// The tensor core only takes fp16 operands from shared memory, so the packed weights cannot go
+// from the TMA ring straight into tcgen05.mma as the fp16 ops do.  Eight warps stand in between:
+// they read a landed stage's packed rows, dequantise them in registers and write fp16 tiles in
+// the layout the TMA would have produced for an fp16 weight (K-major [128 n][64 k], rows of
+// 128 B, 128B swizzle) into one of two 32 KB staging buffers, each holding 128 consecutive k of
+// the 128 output columns.  One thread then issues the MMAs against the staging buffer and the
+// activation boxes of the stage, exactly as fg_umma_kernel does.  With fragments and
+// accumulators out of the register file, dequantisation is the only per-element work left to
+// the SM's issue slots (about 13 instructions per eight int4 weights), which keeps an int4
+// stream (half the bytes of int8 per weight) within what the tensor-core-free part of an SM
+// can convert, where the mma.sync kernel is bound by its fragment traffic and MMA issue.
+//
+//   staging buffer = 128 k:  int8: one 16 KB chunk of the ring;  int4: half a chunk.
+//   Scales are per output channel and stay in the fp32 epilogue, as in the other kernels.  The
+//   kernel can also fold group-wise int4 scales into the dequantisation (one fp16 multiply per
+//   weight), but that rounding costs about 1e-2 absolute at K of a few thousand, which is the
+//   whole tolerance of the path for outputs near zero: the host sends group-wise calls to the
+//   mma.sync kernel, which scales each group's fp32 partial sum instead.
+//
+// Warp roles: 0-3 epilogue, 4 producer (TMA), 5 MMA issue and TMEM allocation, 6-9 finishers
+// (the four warps serve both of a CTA's partial tiles, one after the other), 10-17 dequantise.
+#pragma once
+#include "fg_umma.cuh"
+
+namespace fg {
+
+constexpr int kUmmaQDequantWarps = 8;
+constexpr int kUmmaQThreads = (6 + kUmmaMT / 4 + kUmmaQDequantWarps) * 32;  // 576
+constexpr uint32_t kStagingBytes = 32768;  // fp16 [128 n][128 k]: two K-major sub-tiles of 16 KB
+
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// Eight unsigned 4-bit weights of one word (nibble i = element i) to four half2 in element
+// order, minus the zero point (`magic` = half2(1024 + zero_point), see dequant_u4x8).
+__device__ __forceinline__ void dequant_u4x8_ordered(uint32_t w, uint32_t magic, uint32_t (&out)[4]) {
+  const uint32_t even = w & 0x0F0F0F0Fu;         // bytes: elements 0, 2, 4, 6
+  const uint32_t odd = (w >> 4) & 0x0F0F0F0Fu;   // bytes: elements 1, 3, 5, 7
+  const uint32_t lo = prmt(even, odd, 0x5140);   // bytes: elements 0, 1, 2, 3
+  const uint32_t hi = prmt(even, odd, 0x7362);   // bytes: elements 4, 5, 6, 7
+  const uint32_t e64 = 0x64646464u;
+  uint32_t v[4] = {prmt(lo, e64, 0x5140), prmt(lo, e64, 0x5342), prmt(hi, e64, 0x5140), prmt(hi, e64, 0x5342)};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) asm("sub.f16x2 %0, %1, %2;" : "=r"(out[i]) : "r"(v[i]), "r"(magic));
+}
+
+template <int OP>
+__global__ void __launch_bounds__(kUmmaQThreads, 1)
+    fg_umma_q_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                     const KParams p) {
+  static_assert(OP == kOpW8A16NK || OP == kOpW4A16NK, "quantized weights only");
+  using T = OpTraits<OP>;
+  constexpr int MT = kUmmaMT;
+  constexpr int kHalves = T::chunkK / 128;  // staging buffers per ring chunk: int8 1, int4 2
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+
+  const int S = p.stages;
+  const int cps = p.chunks_per_stage;
+  constexpr int cbytes = chunk_bytes(OP, MT);
+  const uint32_t stage_bytes = cps * cbytes;
+  const uint32_t ring_bytes = S * stage_bytes;
+  const uint32_t staging = smem_base + ring_bytes;              // [2] x 32 KB, 1 KB aligned
+  const uint32_t bar_base = staging + 2 * kStagingBytes;        // full[S], empty[S]
+  const uint32_t bar_acc_full = bar_base + 16 * S;              // [2] MMA -> epilogue
+  const uint32_t bar_acc_empty = bar_acc_full + 16;             // [2] epilogue -> MMA
+  const uint32_t bar_flush = bar_acc_empty + 16;                // [2] epilogue -> finishers (per partial)
+  const uint32_t bar_a_full = bar_flush + 16;                   // [2] dequantisers -> MMA
+  const uint32_t bar_a_empty = bar_a_full + 16;                 // [2] MMA -> dequantisers
+  const uint32_t tmem_slot = bar_a_empty + 16;
+  const uint32_t tail = ring_bytes + 2 * kStagingBytes + 16 * S;
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + 80);
+  volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + 84);  // [2]
+
+  if (blockDim.x != static_cast<unsigned>(kUmmaQThreads) || dynamic_smem_size() < 1023u + tail + 96u) {
+    if (threadIdx.x == 0) atomicExch(p.status, kStatusBadLaunch);
+    return;
+  }
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  unsigned long long* trace = p.trace ? p.trace + kTraceSlots * blockIdx.x : nullptr;
+  if (trace && threadIdx.x == 0) {
+    trace[0] = globaltimer_ns();
+    trace[12] = smid();
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_base + 8 * s, 1);
+      mbar_init(bar_base + 8 * (S + s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 4);
+      mbar_init(bar_flush + 8 * b, 128);
+      mbar_init(bar_a_full + 8 * b, kUmmaQDequantWarps * 32);
+      mbar_init(bar_a_empty + 8 * b, 1);
+    }
+    fence_mbar_init();
+    fence_proxy_async();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  const uint32_t KB = p.k_blocks;
+  const uint32_t total = static_cast<uint32_t>(p.tiles) * KB;
+  const uint32_t G = gridDim.x;
+  const CtaRange range{KB, total, G, range_begin(blockIdx.x, total, G), range_begin(blockIdx.x + 1, total, G)};
+  const uint32_t ub = range.ub, ue = range.ue;
+  const int k_per_stage = cps * T::chunkK;
+
+  if (warp == 4) {
+    if (lane == 0) run_producer<OP, MT>(tmW, tmX, p, range, smem_base, bar_base, S, cps, trace);
+    return;
+  }
+  if (warp >= 6 && warp < 10) {
+    // one set of warps for both partial tiles of the CTA: the first, then the second
+    run_finisher<OP, MT>(p, range, bar_flush, prev_slot, 0, warp - 6, lane, trace);
+    run_finisher<OP, MT>(p, range, bar_flush, prev_slot, 1, warp - 6, lane, trace);
+    return;
+  }
+
+  if (warp >= 10) {
+    // ------------------------------------ dequantise ------------------------------------
+    // Thread d converts 64 k of one weight row per staging buffer: row = d % 128, k half = d / 128.
+    // Consecutive lanes take consecutive rows, whose 16-byte pieces the swizzle spreads over
+    // all banks, for the packed reads as for the fp16 writes.
+    const int d = threadIdx.x - 10 * 32;
+    const int row = d & 127, khalf = d >> 7;
+    const uint32_t sw = static_cast<uint32_t>(row & 7);
+    const bool grouped = (OP == kOpW4A16NK) && p.scale_groups > 1;
+    uint32_t u = ub;
+    int s = 0;
+    uint32_t ph = 0, cnt = 0;
+    bool dead = false;
+    while (u < ue && !dead) {
+      const uint32_t tile = u / KB;
+      const int kb0 = static_cast<int>(u - tile * KB);
+      const int len = static_cast<int>((KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u));
+      for (int it = 0; it < len && !dead; ++it, s = (s + 1 == S) ? 0 : s + 1, ph ^= (s == 0)) {
+        const int k0 = (kb0 + it) * k_per_stage;
+        int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
+        nch = nch < cps ? nch : cps;
+        // group scales of this row for the whole stage, requested before the stage is waited for
+        __half gs[4 * kHalves];
+        if (grouped) {
+#pragma unroll
+          for (int i = 0; i < 4 * kHalves; ++i) {
+            int gi = (k0 >> 7) + i;
+            gi = gi < p.scale_groups ? gi : p.scale_groups - 1;
+            gs[i] = (i < nch * kHalves)
+                        ? __ldg(p.scales + static_cast<size_t>(tile * kTileN + row) * p.scale_groups + gi)
+                        : __half(0.f);
+          }
+        }
+        if (!mbar_wait_bounded(bar_base + 8 * s, ph, kWaitBudgetNs * 2)) {
+          dead = true;
+          break;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {  // at most four chunks per stage; unrolled so that gs[] stays in registers
+          if (c >= nch || dead) break;
+          const uint32_t src_row = smem_base + s * stage_bytes + c * cbytes + row * 128;
+#pragma unroll
+          for (int hf = 0; hf < kHalves; ++hf, ++cnt) {
+            const uint32_t buf = cnt & 1;
+            if (!mbar_wait_bounded(bar_a_empty + 8 * buf, ((cnt >> 1) & 1) ^ 1, kWaitBudgetNs * 2)) {
+              dead = true;
+              break;
+            }
+            const uint32_t dst_row = staging + buf * kStagingBytes + khalf * 16384 + row * 128;
+            if constexpr (OP == kOpW4A16NK) {
+              uint32_t sc2 = 0;
+              if (grouped) {
+                const __half2 h2 = __half2half2(gs[c * kHalves + hf]);
+                sc2 = *reinterpret_cast<const uint32_t*>(&h2);
+              }
+#pragma unroll
+              for (int pc = 0; pc < 2; ++pc) {
+                const uint32_t piece = hf * 4 + khalf * 2 + pc;
+                uint32_t w[4];
+                lds_v4(src_row + ((piece ^ sw) << 4), w[0], w[1], w[2], w[3]);
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+                  uint32_t o[4];
+                  dequant_u4x8_ordered(w[wi], p.w4_magic, o);
+                  if (grouped) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[i] = hmul2_u32(o[i], sc2);
+                  }
+                  sts_v4(dst_row + (((pc * 4 + wi) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int pc = 0; pc < 4; ++pc) {
+                const uint32_t piece = khalf * 4 + pc;
+                uint32_t w[4];
+                lds_v4(src_row + ((piece ^ sw) << 4), w[0], w[1], w[2], w[3]);
+                uint32_t o[8];
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) dequant_s8x4(w[wi], o[2 * wi], o[2 * wi + 1]);
+                sts_v4(dst_row + (((pc * 2) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+                sts_v4(dst_row + (((pc * 2 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+              }
+            }
+            fence_proxy_async();  // these generic-proxy writes are read by the tensor core
+            mbar_arrive(bar_a_full + 8 * buf);
+          }
+        }
+      }
+      u += len;
+    }
+    if (dead && lane == 0) atomicExch(p.status, kStatusTimeout);
+    return;
+  }
+
+  if (warp == 5) {
+    // ------------------------------------ MMA issue ------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(false);
+      constexpr uint64_t a_hi = umma_smem_desc(0, 1, 64);
+      constexpr uint64_t b_hi = umma_smem_desc(0, 1, 64);
+      uint32_t u = ub;
+      uint32_t sg = 0, cnt = 0;
+      bool dead = false;
+      int s = 0;
+      while (u < ue && !dead) {
+        const uint32_t tile = u / KB;
+        const int kb0 = static_cast<int>(u - tile * KB);
+        const int len = static_cast<int>((KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u));
+        const uint32_t b = sg & 1, use = sg >> 1;
+        if (!mbar_wait_bounded(bar_acc_empty + 8 * b, (use & 1) ^ 1, kWaitBudgetNs * 2)) {
+          dead = true;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT);
+        uint32_t acc_flag = 0;
+        for (int it = 0; it < len && !dead; ++it, s = (s + 1 == S) ? 0 : s + 1) {
+          const int k0 = (kb0 + it) * k_per_stage;
+          int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
+          nch = nch < cps ? nch : cps;
+          if (trace && it == 0 && u == ub) trace[3] = globaltimer_ns();
+          for (int c = 0; c < nch && !dead; ++c) {
+            const uint32_t xb = smem_base + s * stage_bytes + c * cbytes + kChunkWBytes;
+#pragma unroll
+            for (int hf = 0; hf < kHalves; ++hf, ++cnt) {
+              const uint32_t buf = cnt & 1;
+              // the staging buffer is complete, which also says that the stage (and with it the
+              // activation boxes) has landed: the dequantisers waited for it
+              if (!mbar_wait_bounded(bar_a_full + 8 * buf, (cnt >> 1) & 1, kWaitBudgetNs * 2)) {
+                dead = true;
+                break;
+              }
+              tc_fence_after_sync();
+              const uint32_t ab = staging + buf * kStagingBytes;
+#pragma unroll
+              for (int t2 = 0; t2 < 2; ++t2) {  // two 64-k sub-tiles, one activation box each
+                const uint64_t a0 = a_hi | ((ab + t2 * 16384) >> 4);
+                const uint64_t b0 = b_hi | ((xb + (hf * 2 + t2) * (MT * 128)) >> 4);
+                umma_f16(tmem_d, a0, b0, idesc, acc_flag);
+                umma_f16(tmem_d + kUmmaMT, a0 + 2, b0 + 2, idesc, acc_flag);
+                umma_f16(tmem_d, a0 + 4, b0 + 4, idesc, 1u);
+                umma_f16(tmem_d + kUmmaMT, a0 + 6, b0 + 6, idesc, 1u);
+                acc_flag = 1u;
+              }
+              umma_commit(bar_a_empty + 8 * buf);
+            }
+          }
+          if (dead) break;
+          umma_commit(bar_base + 8 * (S + s));  // the ring slot is free once these MMAs have read its activations
+        }
+        if (dead) break;
+        umma_commit(bar_acc_full + 8 * b);
+        if (trace) trace[4] = globaltimer_ns();
+        ++sg;
+        u += len;
+      }
+      if (dead) atomicExch(p.status, kStatusTimeout);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------ epilogue warps 0-3 ------------------------------------
+    const int n_in_tile = warp * 32 + lane;
+    uint32_t u = ub;
+    uint32_t sg = 0, ev = 0;
+    bool dead = false;
+    while (u < ue) {
+      const uint32_t tile = u / KB;
+      const uint32_t kb0 = u - tile * KB;
+      const uint32_t len = (KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u);
+      const bool whole = (len == KB);
+      const uint32_t b = sg & 1, use = sg >> 1;
+      uint32_t r[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) r[i] = 0;
+      if (!dead) {
+        bool ok = mbar_wait_bounded(bar_acc_full + 8 * b, use & 1, kWaitBudgetNs * 4);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          dead = true;
+          if (lane == 0) atomicExch(p.status, kStatusTimeout);
+        }
+      }
+      if (!dead) {
+        tc_fence_after_sync();
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * (kUmmaChains * kUmmaMT), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int m = 0; m < MT; ++m) r[m] = __float_as_uint(__uint_as_float(r[m]) + __uint_as_float(r[MT + m]));
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);
+      }
+      const int n = tile * kTileN + n_in_tile;
+      if (whole) {
+        with_act(p.act, [&](auto tag) {
+          constexpr int ACT = decltype(tag)::value;
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m < p.M) store_out1<OP, ACT>(p, m, n, __uint_as_float(r[m]));
+        });
+      } else {
+        const int slot = (u == ub) ? 0 : 1;
+        float* mypart = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MT * kTileN);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) mypart[m * kTileN + n_in_tile] = __uint_as_float(r[m]);
+        mbar_arrive(bar_flush + 8 * ev);
+        ++ev;
+      }
+      if (trace && threadIdx.x == 0) trace[6] += 1;
+      ++sg;
+      u += len;
+    }
+  }
+
+  tc_fence_before_sync();
+  named_bar_sync(2, 160);
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace fg

@@ -78,8 +78,8 @@ def test_plan_invariants(op, M, N, K):
         if op in (2, 3):  # the dequantising kernels: <= 384 threads per CTA
             assert p.consumer_warps <= (3 if p.m_tile == 16 else 4)
     else:
-        assert p.math == 2 and op in (0, 1) and p.m_tile == 16, "tcgen05 kernel: fp16 weights, 16-row accumulator"
-    assert (p.math == 2) == (op in (0, 1) and M > 8), "more than 8 rows of fp16 go to the tcgen05 kernel"
+        assert p.math == 2 and p.m_tile == 16, "tcgen05 kernels: 16-row accumulator in tensor memory"
+    assert (p.math == 2) == (M > 8), "more than 8 token rows go to the tcgen05 kernels"
     assert p.smem_bytes <= 232448
     assert p.passes == -(-M // 16)
     assert capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK
