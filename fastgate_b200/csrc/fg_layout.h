@@ -34,13 +34,13 @@ static inline int fg_smem_bytes(int op, int m_tile, int chunks, int stages, int 
   return fg_fixed_smem_bytes(consumer_warps, m_tile) + stages * (chunks * fg_chunk_bytes(op, m_tile) + 16);
 }
 
-/* tcgen05 variant for quantized weights: ring, two 32 KB fp16 staging buffers, barriers */
+/* tcgen05 variant for quantized weights: ring, 32 KB fp16 staging buffers, barriers */
 #ifdef __cplusplus
 struct fg_plan_t;
 extern "C" int fg_plan_mma_sync(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
                                 struct fg_plan_t* out); /* quantized ops: the mma.sync kernel's plan for any M */
 #endif
-#define FG_UMMA_Q_STAGING_BYTES 65536
+#define FG_UMMA_Q_STAGING_BYTES 98304 /* three 32 KB buffers */
 static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages);
 
 /* tcgen05 variant: ring + barriers only (the accumulators live in tensor memory) */
@@ -48,5 +48,5 @@ static inline int fg_umma_smem_bytes(int op, int chunks, int stages) {
   return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + 64;
 }
 static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages) {
-  return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + FG_UMMA_Q_STAGING_BYTES + 96;
+  return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + FG_UMMA_Q_STAGING_BYTES + 128;
 }

@@ -88,7 +88,7 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
     p.grid = static_cast<int>(std::min<long long>(std::min(sm_count, FG_MAX_GRID), units));
     if (units * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;
     const int stage_bytes = chunks * fg_chunk_bytes(op, 16);
-    p.stages = std::min((smem_optin_bytes - 1024 - 96 - FG_UMMA_Q_STAGING_BYTES) / (stage_bytes + 16), FG_MAX_STAGES);
+    p.stages = std::min((smem_optin_bytes - 1024 - 128 - FG_UMMA_Q_STAGING_BYTES) / (stage_bytes + 16), FG_MAX_STAGES);
     if (p.stages < 2) return FG_ERR_PLAN;
     p.pdl = 1;
     p.smem_bytes = fg_umma_q_smem_bytes(op, chunks, p.stages);

@@ -20,15 +20,20 @@
 //   mma.sync kernel, which scales each group's fp32 partial sum instead.
 //
 // Warp roles: 0-3 epilogue, 4 producer (TMA), 5 MMA issue and TMEM allocation, 6-9 finishers
-// (the four warps serve both of a CTA's partial tiles, one after the other), 10-17 dequantise.
+// (the four warps serve both of a CTA's partial tiles, one after the other), 10-17 dequantise,
+// 18 second MMA issuer (the tensor core takes MMAs from several threads; one thread alone spends
+// about 50 ns per instruction, which at 16 token columns per MMA is the kernel's bottleneck).
 #pragma once
+#include "fg_layout.h"
 #include "fg_umma.cuh"
 
 namespace fg {
 
 constexpr int kUmmaQDequantWarps = 8;
-constexpr int kUmmaQThreads = (6 + kUmmaMT / 4 + kUmmaQDequantWarps) * 32;  // 576
+constexpr int kUmmaQIssuers = 2;  // MMA-issuing threads, one accumulation chain each
+constexpr int kUmmaQThreads = (6 + kUmmaMT / 4 + kUmmaQDequantWarps + (kUmmaQIssuers - 1)) * 32;  // 608
 constexpr uint32_t kStagingBytes = 32768;  // fp16 [128 n][128 k]: two K-major sub-tiles of 16 KB
+constexpr int kNStaging = FG_UMMA_Q_STAGING_BYTES / 32768;  // staging buffers in flight between the dequantisers and the MMA thread
 
 __device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
@@ -68,19 +73,21 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
   constexpr int cbytes = chunk_bytes(OP, MT);
   const uint32_t stage_bytes = cps * cbytes;
   const uint32_t ring_bytes = S * stage_bytes;
-  const uint32_t staging = smem_base + ring_bytes;              // [2] x 32 KB, 1 KB aligned
-  const uint32_t bar_base = staging + 2 * kStagingBytes;        // full[S], empty[S]
+  const uint32_t staging = smem_base + ring_bytes;              // [kNStaging] x 32 KB, 1 KB aligned
+  const uint32_t bar_base = staging + kNStaging * kStagingBytes;  // full[S], empty[S]
   const uint32_t bar_acc_full = bar_base + 16 * S;              // [2] MMA -> epilogue
   const uint32_t bar_acc_empty = bar_acc_full + 16;             // [2] epilogue -> MMA
   const uint32_t bar_flush = bar_acc_empty + 16;                // [2] epilogue -> finishers (per partial)
-  const uint32_t bar_a_full = bar_flush + 16;                   // [2] dequantisers -> MMA
-  const uint32_t bar_a_empty = bar_a_full + 16;                 // [2] MMA -> dequantisers
-  const uint32_t tmem_slot = bar_a_empty + 16;
-  const uint32_t tail = ring_bytes + 2 * kStagingBytes + 16 * S;
-  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + 80);
-  volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + 84);  // [2]
+  const uint32_t bar_a_full = bar_flush + 16;                   // [kNStaging] dequantisers -> MMA
+  const uint32_t bar_a_empty = bar_a_full + 8 * kNStaging;      // [kNStaging] MMA -> dequantisers
+  const uint32_t tmem_slot = bar_a_empty + 8 * kNStaging;
+  const uint32_t tail = ring_bytes + kNStaging * kStagingBytes + 16 * S;
+  constexpr uint32_t kBarBytes = 48 + 16 * kNStaging;           // the barriers after full[] / empty[]
+  volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + kBarBytes);
+  volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + kBarBytes + 4);  // [2]
+  static_assert(kBarBytes + 16 <= 128, "barrier block outgrew its reservation (fg_umma_q_smem_bytes)");
 
-  if (blockDim.x != static_cast<unsigned>(kUmmaQThreads) || dynamic_smem_size() < 1023u + tail + 96u) {
+  if (blockDim.x != static_cast<unsigned>(kUmmaQThreads) || dynamic_smem_size() < 1023u + tail + 128u) {
     if (threadIdx.x == 0) atomicExch(p.status, kStatusBadLaunch);
     return;
   }
@@ -96,14 +103,16 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(bar_base + 8 * s, 1);
-      mbar_init(bar_base + 8 * (S + s), 1);
+      mbar_init(bar_base + 8 * (S + s), kUmmaQIssuers);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_full + 8 * b, kUmmaQIssuers);
       mbar_init(bar_acc_empty + 8 * b, 4);
       mbar_init(bar_flush + 8 * b, 128);
+    }
+    for (int b = 0; b < kNStaging; ++b) {
       mbar_init(bar_a_full + 8 * b, kUmmaQDequantWarps * 32);
-      mbar_init(bar_a_empty + 8 * b, 1);
+      mbar_init(bar_a_empty + 8 * b, kUmmaQIssuers);
     }
     fence_mbar_init();
     fence_proxy_async();
@@ -135,7 +144,7 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
     return;
   }
 
-  if (warp >= 10) {
+  if (warp >= 10 && warp < 10 + kUmmaQDequantWarps) {
     // ------------------------------------ dequantise ------------------------------------
     // Thread d converts 64 k of one weight row per staging buffer: row = d % 128, k half = d / 128.
     // Consecutive lanes take consecutive rows, whose 16-byte pieces the swizzle spreads over
@@ -146,7 +155,8 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
     const bool grouped = (OP == kOpW4A16NK) && p.scale_groups > 1;
     uint32_t u = ub;
     int s = 0;
-    uint32_t ph = 0, cnt = 0;
+    uint32_t ph = 0;
+    uint32_t buf = 0, bph = 0;  // staging buffer in turn and the parity of its use count
     bool dead = false;
     while (u < ue && !dead) {
       const uint32_t tile = u / KB;
@@ -177,9 +187,8 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
           if (c >= nch || dead) break;
           const uint32_t src_row = smem_base + s * stage_bytes + c * cbytes + row * 128;
 #pragma unroll
-          for (int hf = 0; hf < kHalves; ++hf, ++cnt) {
-            const uint32_t buf = cnt & 1;
-            if (!mbar_wait_bounded(bar_a_empty + 8 * buf, ((cnt >> 1) & 1) ^ 1, kWaitBudgetNs * 2)) {
+          for (int hf = 0; hf < kHalves; ++hf) {
+            if (!mbar_wait_bounded(bar_a_empty + 8 * buf, bph ^ 1, kWaitBudgetNs * 2)) {
               dead = true;
               break;
             }
@@ -221,6 +230,10 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
             }
             fence_proxy_async();  // these generic-proxy writes are read by the tensor core
             mbar_arrive(bar_a_full + 8 * buf);
+            if (++buf == kNStaging) {
+              buf = 0;
+              bph ^= 1;
+            }
           }
         }
       }
@@ -230,14 +243,19 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
     return;
   }
 
-  if (warp == 5) {
+  if (warp == 5 || warp >= 10 + kUmmaQDequantWarps) {
     // ------------------------------------ MMA issue ------------------------------------
+    // Issuer i owns accumulation chain i (its own TMEM columns) and the k16 steps i, i + 2 of
+    // every 64-k sub-tile; the issuers never touch the same accumulator, so nothing orders them
+    // against each other, and every hand-off barrier counts one commit per issuer.
+    const int iss = (warp == 5) ? 0 : warp - (10 + kUmmaQDequantWarps) + 1;
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(false);
       constexpr uint64_t a_hi = umma_smem_desc(0, 1, 64);
       constexpr uint64_t b_hi = umma_smem_desc(0, 1, 64);
       uint32_t u = ub;
-      uint32_t sg = 0, cnt = 0;
+      uint32_t sg = 0;
+      uint32_t buf = 0, bph = 0;
       bool dead = false;
       int s = 0;
       while (u < ue && !dead) {
@@ -250,21 +268,20 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
           break;
         }
         tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT);
+        const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT) + iss * kUmmaMT;
         uint32_t acc_flag = 0;
         for (int it = 0; it < len && !dead; ++it, s = (s + 1 == S) ? 0 : s + 1) {
           const int k0 = (kb0 + it) * k_per_stage;
           int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
           nch = nch < cps ? nch : cps;
-          if (trace && it == 0 && u == ub) trace[3] = globaltimer_ns();
+          if (trace && iss == 0 && it == 0 && u == ub) trace[3] = globaltimer_ns();
           for (int c = 0; c < nch && !dead; ++c) {
             const uint32_t xb = smem_base + s * stage_bytes + c * cbytes + kChunkWBytes;
 #pragma unroll
-            for (int hf = 0; hf < kHalves; ++hf, ++cnt) {
-              const uint32_t buf = cnt & 1;
+            for (int hf = 0; hf < kHalves; ++hf) {
               // the staging buffer is complete, which also says that the stage (and with it the
               // activation boxes) has landed: the dequantisers waited for it
-              if (!mbar_wait_bounded(bar_a_full + 8 * buf, (cnt >> 1) & 1, kWaitBudgetNs * 2)) {
+              if (!mbar_wait_bounded(bar_a_full + 8 * buf, bph, kWaitBudgetNs * 2)) {
                 dead = true;
                 break;
               }
@@ -274,13 +291,15 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
               for (int t2 = 0; t2 < 2; ++t2) {  // two 64-k sub-tiles, one activation box each
                 const uint64_t a0 = a_hi | ((ab + t2 * 16384) >> 4);
                 const uint64_t b0 = b_hi | ((xb + (hf * 2 + t2) * (MT * 128)) >> 4);
-                umma_f16(tmem_d, a0, b0, idesc, acc_flag);
-                umma_f16(tmem_d + kUmmaMT, a0 + 2, b0 + 2, idesc, acc_flag);
-                umma_f16(tmem_d, a0 + 4, b0 + 4, idesc, 1u);
-                umma_f16(tmem_d + kUmmaMT, a0 + 6, b0 + 6, idesc, 1u);
+                umma_f16(tmem_d, a0 + 2 * iss, b0 + 2 * iss, idesc, acc_flag);
+                umma_f16(tmem_d, a0 + 2 * iss + 4, b0 + 2 * iss + 4, idesc, 1u);
                 acc_flag = 1u;
               }
               umma_commit(bar_a_empty + 8 * buf);
+              if (++buf == kNStaging) {
+                buf = 0;
+                bph ^= 1;
+              }
             }
           }
           if (dead) break;
@@ -288,13 +307,14 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
         }
         if (dead) break;
         umma_commit(bar_acc_full + 8 * b);
-        if (trace) trace[4] = globaltimer_ns();
+        if (trace && iss == 0) trace[4] = globaltimer_ns();
         ++sg;
         u += len;
       }
       if (dead) atomicExch(p.status, kStatusTimeout);
     }
     __syncwarp();
+    if (warp != 5) return;  // warp 5 stays for the teardown (it owns the TMEM allocation)
   } else {
     // ------------------------------------ epilogue warps 0-3 ------------------------------------
     const int n_in_tile = warp * 32 + lane;

@@ -17,7 +17,7 @@ import torch
 
 from . import capi
 
-OPS = {"kn": capi.FG_OP_F16_KN, "nk": capi.FG_OP_F16_NK, "w8": capi.FG_OP_W8A16_NK}
+OPS = {"kn": capi.FG_OP_F16_KN, "nk": capi.FG_OP_F16_NK, "w8": capi.FG_OP_W8A16_NK, "w4": capi.FG_OP_W4A16_NK}
 
 
 def timeline(op: int, M: int, N: int, K: int, pdl: int = 0, copies: int = 3, math: int = -1, chunks: int = 0,
@@ -30,6 +30,8 @@ def timeline(op: int, M: int, N: int, K: int, pdl: int = 0, copies: int = 3, mat
     x = torch.randn(M, K, device=dev).half()
     if op == capi.FG_OP_W8A16_NK:
         Ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev) for _ in range(copies)]
+    elif op == capi.FG_OP_W4A16_NK:
+        Ws = [torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev) for _ in range(copies)]
     elif op == capi.FG_OP_F16_KN:
         Ws = [(torch.randn(K, N, device=dev) / K ** 0.5).half() for _ in range(copies)]
     else:
