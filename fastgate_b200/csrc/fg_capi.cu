@@ -66,7 +66,7 @@ struct DeviceInfo {
   int smem_optin = 0;
   int cc_major = 0;
   int smem_set[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
-  int smem_set_umma[4] = {0, 0, 0, 0};
+  int smem_set_umma[4][3] = {};
   int smem_set_group[2] = {0, 0};
   int smem_set_chain[2] = {0, 0};
 };
@@ -147,10 +147,14 @@ KernelFn pick_kernel(int op, int m_tile) {
   }
 }
 
-KernelFn pick_umma_kernel(int op) {
+KernelFn pick_umma_kernel(int op, int m_tile) {
   if (op == FG_OP_W8A16_NK) return fg::fg_umma_q_kernel<fg::kOpW8A16NK>;
   if (op == FG_OP_W4A16_NK) return fg::fg_umma_q_kernel<fg::kOpW4A16NK>;
-  return op == FG_OP_F16_KN ? fg::fg_umma_kernel<fg::kOpF16KN> : fg::fg_umma_kernel<fg::kOpF16NK>;
+  if (op == FG_OP_F16_KN)
+    return m_tile == 64 ? fg::fg_umma_kernel<fg::kOpF16KN, 64>
+                        : m_tile == 32 ? fg::fg_umma_kernel<fg::kOpF16KN, 32> : fg::fg_umma_kernel<fg::kOpF16KN, 16>;
+  return m_tile == 64 ? fg::fg_umma_kernel<fg::kOpF16NK, 64>
+                      : m_tile == 32 ? fg::fg_umma_kernel<fg::kOpF16NK, 32> : fg::fg_umma_kernel<fg::kOpF16NK, 16>;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -170,8 +174,9 @@ int check_common(const void* x, const void* W, const void* C, int M, int N, int 
 // so a plan can never be launched with another kernel's thread count or memory layout.
 int prepare_kernel(const fg_plan_t& pl, DeviceInfo* dev, KernelFn* out) {
   const bool umma = (pl.math == 2);
-  KernelFn kern = umma ? pick_umma_kernel(pl.op) : pick_kernel(pl.op, pl.m_tile);
-  int& set = umma ? dev->smem_set_umma[pl.op] : dev->smem_set[pl.op][pl.m_tile == 16];
+  KernelFn kern = umma ? pick_umma_kernel(pl.op, pl.m_tile) : pick_kernel(pl.op, pl.m_tile);
+  int& set = umma ? dev->smem_set_umma[pl.op][pl.m_tile == 64 ? 2 : pl.m_tile == 32 ? 1 : 0]
+                  : dev->smem_set[pl.op][pl.m_tile == 16];
   if (pl.smem_bytes > set) {
     const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
@@ -288,8 +293,9 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     }
   }
 
-  for (int m0 = 0; m0 < M; m0 += 16) {
-    const int mp = (M - m0) < 16 ? (M - m0) : 16;
+  const int rows = fg_pass_rows(op, pl.math);  // token rows per launch
+  for (int m0 = 0; m0 < M; m0 += rows) {
+    const int mp = (M - m0) < rows ? (M - m0) : rows;
     if (mp > pl.m_tile) return FG_ERR_PLAN;
     const __half* xp = static_cast<const __half*>(x) + static_cast<size_t>(m0) * K;
     CUtensorMap tmX;
@@ -332,7 +338,7 @@ constexpr int kNoAllocMaxGrid = 160;  // persistent CTAs (a B200 has 148 SMs)
 constexpr size_t kNoAllocTicketsOffset = 256;
 constexpr size_t kNoAllocPartialsOffset = kNoAllocTicketsOffset + 4 * (kNoAllocMaxN / 128);
 constexpr size_t kNoAllocBytes =
-    kNoAllocPartialsOffset + static_cast<size_t>(kNoAllocMaxGrid) * 2 * FG_WS_PARTIAL_TILE_BYTES;
+    kNoAllocPartialsOffset + static_cast<size_t>(kNoAllocMaxGrid) * 2 * FG_WS_PARTIAL_TILE16_BYTES;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
 
 // In host code `g_noalloc_scratch` is only a handle for the symbol, not a device address;
@@ -434,7 +440,10 @@ int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const v
   DeviceInfo* dev = nullptr;
   if ((st = device_info(&dev)) != FG_OK) return st;
   if ((st = fg_plan_validate(plan, N, K, dev->smem_optin)) != FG_OK) return st;
-  if (plan->passes != (M + 15) / 16) return FG_ERR_PLAN;
+  {
+    const int rows = fg_pass_rows(plan->op, plan->math);
+    if (plan->passes != (M + rows - 1) / rows) return FG_ERR_PLAN;
+  }
   return run_planned(*plan, dev, x, W, plan->op == FG_OP_W8A16_NK ? scales : nullptr, C, M, N, K, ws,
                      reinterpret_cast<cudaStream_t>(stream));
 }
@@ -774,7 +783,7 @@ int fg_chain_create(int op, const fg_layer_t* layers, int count, void* table_dev
   ch->grid = grid;
   ch->smem_bytes = fg_umma_smem_bytes(op, chunks, stages) + 32;
   // header | grid x 4 partial tiles | one ticket per tile | one counter per layer | timestamps
-  ch->off_tickets = FG_WS_HEADER_BYTES + static_cast<size_t>(grid) * 4 * FG_WS_PARTIAL_TILE_BYTES;
+  ch->off_tickets = FG_WS_HEADER_BYTES + static_cast<size_t>(grid) * 4 * FG_WS_PARTIAL_TILE16_BYTES;
   ch->off_done = (ch->off_tickets + 4 * static_cast<size_t>(tile) + 255) & ~static_cast<size_t>(255);
   ch->off_trace = (ch->off_done + 4 * static_cast<size_t>(count) + 255) & ~static_cast<size_t>(255);
   ch->ws_bytes = (ch->off_trace + 64 * static_cast<size_t>(count) * grid + 255) & ~static_cast<size_t>(255);

@@ -582,7 +582,7 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
 // order, which keeps the result bit-reproducible.  The consumers meanwhile go on streaming.
 constexpr int kFinBarrier = 3;
 template <int MT>
-__host__ __device__ constexpr int finisher_warps() { return MT / 4; }
+__host__ __device__ constexpr int finisher_warps() { return MT < 16 ? MT / 4 : 4; }  // taller tiles: 16 rows at a time
 
 template <int OP, int MT>
 __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r, uint32_t bar_flush,
@@ -623,8 +623,8 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
       if (prev == c_last - c_first) {
         __threadfence();
         const int n0 = tile * kTileN + 4 * lane;
-        const int m0 = 4 * fin_warp;
-        if (m0 < p.M) {
+#pragma unroll 1
+        for (int m0 = 4 * fin_warp; m0 < MT && m0 < p.M; m0 += 4 * FW) {
           float4 sum[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -11,10 +11,12 @@
 #define FG_CHUNK_W_BYTES 16384     /* weight bytes per chunk                            */
 #define FG_RED_STRIDE 132          /* floats per row of the cross-warp reduction buffer */
 
-/* Workspace: [0,256) status word; then FG_MAX_GRID x 2 partial tiles of 16 x 128 fp32;
+/* Workspace: [0,256) status word; then FG_MAX_GRID x 2 partial tiles of up to 64 x 128 fp32;
  * then one 32-bit arrival counter per output tile. */
 #define FG_WS_HEADER_BYTES 256
-#define FG_WS_PARTIAL_TILE_BYTES (16 * FG_TILE_N * 4)
+#define FG_MAX_M_TILE 64           /* tallest accumulator tile (tcgen05 fp16 kernel)    */
+#define FG_WS_PARTIAL_TILE_BYTES (FG_MAX_M_TILE * FG_TILE_N * 4)
+#define FG_WS_PARTIAL_TILE16_BYTES (16 * FG_TILE_N * 4) /* kernels that never exceed 16 rows */
 #define FG_WS_PARTIALS_BYTES ((size_t)FG_MAX_GRID * 2 * FG_WS_PARTIAL_TILE_BYTES)
 #define FG_WS_TICKETS_OFFSET (FG_WS_HEADER_BYTES + FG_WS_PARTIALS_BYTES)
 
@@ -44,9 +46,14 @@ extern "C" int fg_plan_mma_sync(int op, int M, int N, int K, int sm_count, int s
 static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages);
 
 /* tcgen05 variant: ring + barriers only (the accumulators live in tensor memory) */
-static inline int fg_umma_smem_bytes(int op, int chunks, int stages) {
-  return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + 64;
+static inline int fg_umma_smem_bytes_mt(int op, int m_tile, int chunks, int stages) {
+  return 1024 + stages * (chunks * fg_chunk_bytes(op, m_tile) + 16) + 64;
 }
+static inline int fg_umma_smem_bytes(int op, int chunks, int stages) {
+  return fg_umma_smem_bytes_mt(op, 16, chunks, stages);
+}
+/* token rows one launch covers: 64 for the fp16 tcgen05 kernel, 16 otherwise */
+static inline int fg_pass_rows(int op, int math) { return (math == 2 && op <= 1) ? FG_MAX_M_TILE : 16; }
 static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages) {
   return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + FG_UMMA_Q_STAGING_BYTES + 128;
 }

@@ -37,16 +37,21 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
   fg_plan_t p;
   std::memset(&p, 0, sizeof(p));
   p.op = op;
+  const bool quantized = (op == FG_OP_W8A16_NK || op == FG_OP_W4A16_NK);
   p.passes = (M + 15) / 16;
   // accumulator tile height of the (last) pass; earlier passes of a multi-pass call use 16
   const int m_last = M - (p.passes - 1) * 16;
   p.m_tile = (p.passes == 1 && m_last <= 8) ? 8 : 16;
+  if (!quantized && M > 16) {
+    // fp16 weights: the tcgen05 kernel takes up to 64 token rows per pass over the weight
+    p.passes = (M + FG_MAX_M_TILE - 1) / FG_MAX_M_TILE;
+    p.m_tile = (M <= 32) ? 32 : 64;
+  }
   p.math = 0;
   p.tiles = N / 128;
 
   const int chunk_k = fg_chunk_k(op);
-  const bool quantized = (op == FG_OP_W8A16_NK || op == FG_OP_W4A16_NK);
-  if (!quantized && p.m_tile == 16) {
+  if (!quantized && p.m_tile >= 16) {
     // fp16 weights, more than 8 token rows: the tcgen05 kernel (accumulator in tensor memory,
     // no cross-warp reduction, the whole shared memory is ring).  Its single MMA-issuing
     // thread pays a fixed cost per stage, so stages are as large as the work allows:
@@ -64,11 +69,23 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
     const long long units = static_cast<long long>(p.tiles) * p.k_blocks;
     p.grid = static_cast<int>(std::min<long long>(std::min(sm_count, FG_MAX_GRID), units));
     if (units * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;
-    const int stage_bytes = chunks * fg_chunk_bytes(op, 16);
+    int stage_bytes = chunks * fg_chunk_bytes(op, p.m_tile);
     p.stages = std::min((smem_optin_bytes - 1024 - 64) / (stage_bytes + 16), FG_MAX_STAGES);
+    while (p.stages < 3 && chunks > 1) {  // taller activation tiles: smaller stages keep the ring three deep
+      chunks >>= 1;
+      p.k_per_stage = chunks * chunk_k;
+      p.k_blocks = (K + p.k_per_stage - 1) / p.k_per_stage;
+      stage_bytes = chunks * fg_chunk_bytes(op, p.m_tile);
+      p.stages = std::min((smem_optin_bytes - 1024 - 64) / (stage_bytes + 16), FG_MAX_STAGES);
+    }
     if (p.stages < 2) return FG_ERR_PLAN;
+    {
+      const long long units2 = static_cast<long long>(p.tiles) * p.k_blocks;
+      p.grid = static_cast<int>(std::min<long long>(std::min(sm_count, FG_MAX_GRID), units2));
+      if (units2 * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;
+    }
     p.pdl = 1;
-    p.smem_bytes = fg_umma_smem_bytes(op, chunks, p.stages);
+    p.smem_bytes = fg_umma_smem_bytes_mt(op, p.m_tile, chunks, p.stages);
     *out = p;
     return FG_OK;
   }
@@ -134,7 +151,8 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (smem_optin_bytes <= 0) smem_optin_bytes = 232448;
   if (p->op < FG_OP_F16_KN || p->op > FG_OP_W4A16_NK) return FG_ERR_PLAN;
   const bool quantized = (p->op == FG_OP_W8A16_NK || p->op == FG_OP_W4A16_NK);
-  if (p->m_tile != 8 && p->m_tile != 16) return FG_ERR_PLAN;
+  if (p->m_tile != 8 && p->m_tile != 16 && p->m_tile != 32 && p->m_tile != 64) return FG_ERR_PLAN;
+  if (p->m_tile > 16 && (p->math != 2 || p->op > FG_OP_F16_NK)) return FG_ERR_PLAN;  // tall tiles: fp16 tcgen05 kernel only
   if (p->math != 0 && p->math != 2) return FG_ERR_PLAN;
   const int chunk_k = fg_chunk_k(p->op);
   if (p->k_per_stage <= 0 || p->k_per_stage % chunk_k) return FG_ERR_PLAN;
@@ -143,8 +161,8 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (p->stages < 2 || p->stages > FG_MAX_STAGES) return FG_ERR_PLAN;
   if (p->math == 2) {
     // tcgen05 variants: 16-row accumulator in tensor memory, fixed warp roles
-    if (p->m_tile != 16) return FG_ERR_PLAN;
-    if (quantized && chunks > 4) return FG_ERR_PLAN;
+    if (p->m_tile < 16) return FG_ERR_PLAN;
+    if (quantized && (chunks > 4 || p->m_tile != 16)) return FG_ERR_PLAN;
   } else {
     if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
     // the dequantising kernels are built for <= 4 consumer warps (<= 3 with a 16-row tile)
@@ -158,7 +176,7 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (p->grid < 1 || p->grid > FG_MAX_GRID || p->grid > units) return FG_ERR_PLAN;
   if (units * p->grid >= (1LL << 31)) return FG_ERR_PLAN;  // the kernel's index math is 32-bit
   const int want_smem = (p->math == 2) ? (quantized ? fg_umma_q_smem_bytes(p->op, chunks, p->stages)
-                                                    : fg_umma_smem_bytes(p->op, chunks, p->stages))
+                                                    : fg_umma_smem_bytes_mt(p->op, p->m_tile, chunks, p->stages))
                                        : fg_smem_bytes(p->op, p->m_tile, chunks, p->stages, p->consumer_warps);
   if (p->smem_bytes != want_smem) return FG_ERR_PLAN;
   if (p->smem_bytes > smem_optin_bytes) return FG_ERR_PLAN;

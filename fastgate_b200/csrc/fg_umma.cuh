@@ -20,11 +20,11 @@
 
 namespace fg {
 
-constexpr int kUmmaMT = 16;            // token rows of the accumulator (UMMA N)
-constexpr int kUmmaThreads = (6 + 2 * (kUmmaMT / 4)) * 32;   // two finisher teams (see run_finisher)
+constexpr int kUmmaMT = 16;            // token rows of the accumulator (UMMA N) of the grouped, chained and quantized kernels
+constexpr int kUmmaThreads = (6 + 2 * 4) * 32;             // two finisher teams of four warps (see run_finisher)
 constexpr int kUmmaGroupThreads = (6 + kUmmaMT / 4) * 32;  // grouped and chained kernels: one team
 constexpr int kUmmaChains = 2;         // independent accumulation chains per tile (summed in the epilogue)
-constexpr uint32_t kTmemCols = 64;     // 2 buffers x 2 chains x 16 columns
+constexpr uint32_t kTmemCols = 64;     // 2 buffers x 2 chains x 16 columns (16-row kernels)
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
@@ -80,8 +80,17 @@ __host__ __device__ constexpr uint64_t umma_smem_desc(uint32_t smem_addr, uint32
 }
 // Instruction descriptor, kind::f16: fp16 A and B, fp32 D, M = 128, N = 16, B K-major,
 // A K-major (NxK weight) or MN-major (KxN weight).
-__host__ __device__ constexpr uint32_t umma_idesc(bool a_mn_major) {
-  return (1u << 4) | ((a_mn_major ? 1u : 0u) << 15) | ((kUmmaMT >> 3) << 17) | ((kTileN >> 4) << 24);
+__host__ __device__ constexpr uint32_t umma_idesc(bool a_mn_major, int n = kUmmaMT) {
+  return (1u << 4) | ((a_mn_major ? 1u : 0u) << 15) | ((static_cast<uint32_t>(n) >> 3) << 17) | ((kTileN >> 4) << 24);
+}
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
 }
 
 // One output element of row m, column n (scale, round, store; push-aware like store_out2).
@@ -99,13 +108,17 @@ __device__ __forceinline__ void store_out1(const KParams& p, int m, int n, float
   }
 }
 
-template <int OP>
+// MT = token rows of the accumulator = N of the MMA instruction: 16, 32 or 64.  Up to 64 rows of
+// activations ride along with one pass over the weight; the instruction count, and with it the
+// issuing thread's time, does not depend on MT.
+template <int OP, int MT>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
     fg_umma_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    const KParams p) {
   static_assert(OP == kOpF16KN || OP == kOpF16NK, "tcgen05 path: fp16 weights only");
+  static_assert(MT == 16 || MT == 32 || MT == 64, "accumulator height");
   using T = OpTraits<OP>;
-  constexpr int MT = kUmmaMT;
+  constexpr uint32_t kCols = 2 * kUmmaChains * MT;  // TMEM columns: 2 buffers x 2 chains x MT (64, 128 or 256)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -150,7 +163,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     fence_proxy_async();
   }
   if (warp == 5) {
-    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_alloc(tmem_slot, kCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -182,7 +195,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
     // them to the slot's empty barrier.  The mbarrier wait orders the TMA's writes before
     // the MMA's reads; tcgen05 fences are only needed around the accumulator hand-off.
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(OP == kOpF16KN);
+      constexpr uint32_t idesc = umma_idesc(OP == kOpF16KN, MT);
       uint32_t u = ub;
       int it0 = 0;
       uint32_t sg = 0;
@@ -201,7 +214,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
         tc_fence_after_sync();
         // Even and odd k16 steps accumulate into two separate TMEM tiles: consecutive MMAs
         // then do not wait for each other's accumulator; the epilogue adds the two.
-        const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT);
+        const uint32_t tmem_d = tmem_base + b * (kUmmaChains * MT);
         for (int it = it0; it < it0 + len; ++it, s = (s + 1 == S) ? 0 : s + 1, ph ^= (s == 0)) {
           const unsigned long long tw0 = trace ? globaltimer_ns() : 0;
           if (!mbar_wait_bounded(bar_base + 8 * s, ph, kWaitBudgetNs)) {
@@ -230,9 +243,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
             const uint64_t a0 = a_hi | (wb >> 4);
             const uint64_t b0 = b_hi | ((wb + kChunkWBytes) >> 4);
             umma_f16(tmem_d, a0, b0, idesc, acc_flag);
-            umma_f16(tmem_d + kUmmaMT, a0 + a_step, b0 + 2, idesc, acc_flag);
+            umma_f16(tmem_d + MT, a0 + a_step, b0 + 2, idesc, acc_flag);
             umma_f16(tmem_d, a0 + 2 * a_step, b0 + 4, idesc, 1u);
-            umma_f16(tmem_d + kUmmaMT, a0 + 3 * a_step, b0 + 6, idesc, 1u);
+            umma_f16(tmem_d + MT, a0 + 3 * a_step, b0 + 6, idesc, 1u);
             acc_flag = 1u;
             wb += cbytes;
           }
@@ -261,9 +274,6 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       const uint32_t len = (KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u);
       const bool whole = (len == KB);
       const uint32_t b = sg & 1, use = sg >> 1;
-      uint32_t r[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) r[i] = 0;
       const unsigned long long te0 = (trace && threadIdx.x == 0) ? globaltimer_ns() : 0;
       if (!dead) {
         bool ok = mbar_wait_bounded(bar_acc_full + 8 * b, use & 1, kWaitBudgetNs * 2);
@@ -273,38 +283,61 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           if (lane == 0) atomicExch(p.status, kStatusTimeout);
         }
       }
-      if (!dead) {
-        tc_fence_after_sync();
-        tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * (kUmmaChains * kUmmaMT), r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int m = 0; m < MT; ++m) r[m] = __float_as_uint(__uint_as_float(r[m]) + __uint_as_float(r[MT + m]));
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);  // the MMA warp may reuse this accumulator
-      }
-      if (trace && threadIdx.x == 0) {
-        trace[7] = globaltimer_ns();  // accumulator read back
-        trace[11] += trace[7] - te0;  // waiting for it
-      }
+      if (!dead) tc_fence_after_sync();
       const int n = tile * kTileN + n_in_tile;
-      if (whole) {
-        with_act(p.act, [&](auto tag) {
-          constexpr int ACT = decltype(tag)::value;
+      const int slot = (u == ub) ? 0 : 1;
+      float* mypart = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MT * kTileN);
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * (kUmmaChains * MT);
+      // sixteen token rows at a time: the two chains' columns, summed, then stored or parked
 #pragma unroll
-          for (int m = 0; m < MT; ++m)
-            if (m < p.M) store_out1<OP, ACT>(p, m, n, __uint_as_float(r[m]));
-        });
+      for (int mg = 0; mg < MT / 16; ++mg) {
+        uint32_t r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = 0;
+        if (!dead) {
+          if constexpr (MT == 16) {
+            uint32_t q[32];
+            tmem_ld32(tbase, q);
+            tmem_ld_wait();
+#pragma unroll
+            for (int m = 0; m < 16; ++m) r[m] = __float_as_uint(__uint_as_float(q[m]) + __uint_as_float(q[16 + m]));
+          } else {
+            uint32_t q0[16], q1[16];
+            tmem_ld16(tbase + mg * 16, q0);
+            tmem_ld16(tbase + MT + mg * 16, q1);
+            tmem_ld_wait();
+#pragma unroll
+            for (int m = 0; m < 16; ++m) r[m] = __float_as_uint(__uint_as_float(q0[m]) + __uint_as_float(q1[m]));
+          }
+          if (mg == MT / 16 - 1) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * b);  // the MMA warp may reuse this accumulator
+          }
+        }
+        if (trace && threadIdx.x == 0 && mg == MT / 16 - 1) {
+          trace[7] = globaltimer_ns();  // accumulator read back
+          trace[11] += trace[7] - te0;  // waiting for it
+        }
+        if (whole) {
+          with_act(p.act, [&](auto tag) {
+            constexpr int ACT = decltype(tag)::value;
+#pragma unroll
+            for (int m = 0; m < 16; ++m)
+              if (mg * 16 + m < p.M) store_out1<OP, ACT>(p, mg * 16 + m, n, __uint_as_float(r[m]));
+          });
+        } else {
+#pragma unroll
+          for (int m = 0; m < 16; ++m) mypart[(mg * 16 + m) * kTileN + n_in_tile] = __uint_as_float(r[m]);
+        }
+      }
+      if (whole) {
         if (p.world > 0) {
           __threadfence_system();
           named_bar_sync(1, 128);
           if (threadIdx.x == 0) signal_tile_delivered(p);
         }
       } else {
-        const int slot = (u == ub) ? 0 : 1;
-        float* mypart = p.partials + (static_cast<size_t>(blockIdx.x) * 2 + slot) * (MT * kTileN);
-#pragma unroll
-        for (int m = 0; m < MT; ++m) mypart[m * kTileN + n_in_tile] = __uint_as_float(r[m]);
         mbar_arrive(bar_flush + 8 * ev);
         ++ev;
       }
@@ -319,7 +352,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   named_bar_sync(2, 160);
   if (warp == 5) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, kCols);
   }
 }
 

@@ -61,14 +61,17 @@ SHAPES = [(1, 16, 8192, 8192), (1, 1, 11008, 4096), (1, 1, 4096, 11008), (0, 8, 
           (2, 1, 28672, 8192), (2, 8, 28672, 8192), (1, 16, 9216, 3072), (1, 16, 3072, 3072),
           (1, 16, 12288, 3072), (1, 16, 3072, 12288), (1, 4, 128, 128), (0, 3, 256, 384),
           (1, 16, 1152, 3072), (1, 16, 384, 3072), (1, 16, 1536, 3072), (1, 33, 4096, 4096),
-          (3, 1, 28672, 8192), (3, 16, 28672, 8192), (3, 8, 256, 384), (2, 16, 4096, 4096)]
+          (3, 1, 28672, 8192), (3, 16, 28672, 8192), (3, 8, 256, 384), (2, 16, 4096, 4096),
+          (1, 17, 8192, 8192), (1, 32, 8192, 8192), (0, 48, 4096, 4096), (1, 64, 8192, 8192), (1, 100, 3072, 3072),
+          (2, 40, 4096, 4096)]
 
 
 @pytest.mark.parametrize("op,M,N,K", SHAPES)
 def test_plan_invariants(op, M, N, K):
     p = capi.plan(op, M, N, K, **B200)
     assert p.op == op and p.tiles == N // 128
-    assert p.m_tile in (8, 16) and (p.m_tile == 16 or M <= 8)
+    assert p.m_tile in (8, 16, 32, 64) and (p.m_tile >= 16 or M <= 8)
+    assert p.m_tile <= 16 or (op in (0, 1) and p.math == 2), "tall tiles: fp16 tcgen05 kernel only"
     assert p.k_per_stage % CHUNK_K[op] == 0
     assert p.k_blocks == -(-K // p.k_per_stage)
     assert 1 <= p.grid <= min(148, p.tiles * p.k_blocks)
@@ -78,10 +81,13 @@ def test_plan_invariants(op, M, N, K):
         if op in (2, 3):  # the dequantising kernels: <= 384 threads per CTA
             assert p.consumer_warps <= (3 if p.m_tile == 16 else 4)
     else:
-        assert p.math == 2 and p.m_tile == 16, "tcgen05 kernels: 16-row accumulator in tensor memory"
+        assert p.math == 2 and p.m_tile >= 16, "tcgen05 kernels: accumulator in tensor memory"
+        assert p.stages >= 3 or p.k_per_stage == CHUNK_K[op]
     assert (p.math == 2) == (M > 8), "more than 8 token rows go to the tcgen05 kernels"
     assert p.smem_bytes <= 232448
-    assert p.passes == -(-M // 16)
+    rows = 64 if (p.math == 2 and op in (0, 1)) else 16
+    assert p.passes == -(-M // rows)
+    assert p.m_tile >= min(M, rows) or p.passes > 1
     assert capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK
     simulate(p.tiles, p.k_blocks, p.grid)
 
