@@ -142,6 +142,11 @@ def plan(op: int, M: int, N: int, K: int, sm_count: int = 0, smem_optin: int = 0
     return p
 
 
+def passes(op: int, M: int, N: int, K: int) -> int:
+    """Launches one call makes (a pass covers up to 64 token rows of fp16 weights, 16 otherwise)."""
+    return plan(op, M, N, K).passes
+
+
 def workspace_bytes(N: int) -> int:
     return int(lib.fg_workspace_bytes(N))
 

@@ -23,6 +23,7 @@ from typing import Callable, Optional
 import torch
 import torch.distributed as dist
 
+from . import capi
 from . import workloads as wl
 
 
@@ -144,7 +145,8 @@ class ShardedLinear:
         pb = self.push_buffers(max(M, 16), x.device)
         wait_ptr, wait_target = (after.flag_ptrs[after.rank], after.target) if after is not None else (0, 0)
         ops.linear_nk_push(x, self.w, pb.c_ptrs, pb.flag_ptrs, pb.rank, self.n_total, wait_ptr, wait_target)
-        pb.target += (self.w.shape[0] // 128) * ((M + 15) // 16)
+        # every pass over the weight delivers all of this rank's tiles once
+        pb.target += (self.w.shape[0] // 128) * capi.passes(capi.FG_OP_F16_NK, M, self.w.shape[0], self.w.shape[1])
         if wait:
             self.push_wait(pb)
         return pb.out[:M]

@@ -148,5 +148,6 @@ def test_launches_are_counted(dev):
     C = torch.zeros(8, 512, dtype=torch.half, device=dev)
     n0 = fg.launch_count()
     fg.fastgemv_extend(W, x, C)
-    fg.fastgemv_extend(W, torch.cat([x] * 3), torch.zeros(24, 512, dtype=torch.half, device=dev))  # two passes
-    assert fg.launch_count() - n0 == 3
+    fg.fastgemv_extend(W, torch.cat([x] * 3), torch.zeros(24, 512, dtype=torch.half, device=dev))  # 24 rows: one pass
+    fg.fastgemv_extend(W, torch.cat([x] * 9), torch.zeros(72, 512, dtype=torch.half, device=dev))  # 72 rows: 64 + 8
+    assert fg.launch_count() - n0 == 4

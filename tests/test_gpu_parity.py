@@ -182,10 +182,18 @@ def test_linearity_and_row_independence(dev, ws):
     xd, Wd = x.to(dev), W.to(dev)
     full = torch.zeros(40, 8192, dtype=torch.float16, device=dev)
     assert gu.call(wl.OP_NK, xd, Wd, None, full, 40, 8192, 8192, ws) == capi.FG_OK
-    for (a, b) in [(0, 16), (3, 19), (16, 32), (7, 16), (24, 40), (31, 40)]:  # 16-row tiles, like the full call
+    for (a, b) in [(0, 40), (0, 33), (5, 40), (2, 39)]:  # 64-row tiles, like the full call
         part = torch.zeros(b - a, 8192, dtype=torch.float16, device=dev)
         assert gu.call(wl.OP_NK, xd[a:b].contiguous(), Wd, None, part, b - a, 8192, 8192, ws) == capi.FG_OK
         assert torch.equal(part.view(torch.int16), full[a:b].view(torch.int16)), (a, b)
+    sixteen = torch.zeros(16, 8192, dtype=torch.float16, device=dev)
+    assert gu.call(wl.OP_NK, xd[0:16].contiguous(), Wd, None, sixteen, 16, 8192, 8192, ws) == capi.FG_OK
+    assert _one_rounding_step_apart(sixteen, full[0:16])
+    for (a, b) in [(3, 19), (7, 16), (0, 9)]:  # 16-row tiles among themselves
+        part = torch.zeros(b - a, 8192, dtype=torch.float16, device=dev)
+        assert gu.call(wl.OP_NK, xd[a:b].contiguous(), Wd, None, part, b - a, 8192, 8192, ws) == capi.FG_OK
+        lo, hi = max(a, 0), min(b, 16)
+        assert torch.equal(part[lo - a:hi - a].view(torch.int16), sixteen[lo:hi].view(torch.int16)), (a, b)
     for (a, b) in [(0, 1), (0, 8), (3, 4), (39, 40)]:  # 8-row tiles
         part = torch.zeros(b - a, 8192, dtype=torch.float16, device=dev)
         assert gu.call(wl.OP_NK, xd[a:b].contiguous(), Wd, None, part, b - a, 8192, 8192, ws) == capi.FG_OK
@@ -280,31 +288,34 @@ def test_plan_walk(op, dev, ws):
     assert tried >= 30
 
 
-def _edited_umma(base, N, K, op, chunks, stages, grid, pdl):
+def _edited_umma(base, N, K, op, chunks, stages, grid, pdl, m_tile=16):
     p = capi.Plan()
     ctypes.memmove(ctypes.byref(p), ctypes.byref(base), ctypes.sizeof(p))
-    p.m_tile, p.math, p.consumer_warps, p.pdl = 16, 2, 4, pdl
+    p.m_tile, p.math, p.consumer_warps, p.pdl = m_tile, 2, 4, pdl
     p.k_per_stage = chunks * 64
     p.k_blocks = -(-K // p.k_per_stage)
     p.stages = stages
     p.grid = min(grid, p.tiles * p.k_blocks)
-    p.smem_bytes = 1024 + stages * (chunks * 18432 + 16) + 64
+    p.smem_bytes = 1024 + stages * (chunks * (16384 + m_tile * 128) + 16) + 64
     return p if capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK else None
 
 
 @pytest.mark.parametrize("op", [wl.OP_KN, wl.OP_NK])
 def test_plan_walk_tcgen05(op, dev, ws):
-    """The tcgen05 kernel over ring depths, stage sizes, grid sizes, with and without PDL,
-    for every M (it serves any M <= 16 per pass; the planner only picks it above 8)."""
+    """The tcgen05 kernel over ring depths, stage sizes, grid sizes, tile heights, with and
+    without PDL, for every M (any tile height serves any smaller M; the planner only picks the
+    kernel above 8 rows and the smallest tile that holds the call)."""
     N, K = 1152, 2304
     tried = 0
-    for M in (1, 5, 8, 11, 16, 21):
+    for M, m_tile in ((1, 16), (5, 64), (8, 16), (11, 32), (16, 16), (21, 32)):
         case = wl.Case(f"umma_walk_op{op}_M{M}", op, M, N, K, 61 + M)
         base = capi.plan(op, M, N, K, 148, 232448)
         for chunks, stages, grid, pdl in [(1, 2, 148, 0), (1, 12, 148, 1), (2, 6, 148, 1), (4, 3, 148, 0), (3, 4, 17, 1),
                                           (1, 5, 1, 0), (2, 2, 148, 1), (1, 7, 97, 0)]:
-            p = _edited_umma(base, N, K, op, chunks, stages, grid, pdl)
-            assert p is not None
+            if m_tile > 16 and chunks * (16384 + m_tile * 128) * stages > 220000:
+                stages = 2  # the taller activation boxes leave room for fewer of the large stages
+            p = _edited_umma(base, N, K, op, chunks, stages, grid, pdl, m_tile)
+            assert p is not None, (M, m_tile, chunks, stages)
             run_case(case, dev, ws, plan=p, check_twice=(tried % 5 == 0))
             tried += 1
     assert tried == 48

@@ -50,7 +50,7 @@ def test_single_rank_push_equals_plain(M, N, K, dev):
     for rep in range(2):
         st = L.fg_gemm_f16_nk_push(x.data_ptr(), W.data_ptr(), M, N, K, ctypes.byref(peers), ws.ptr, ws.bytes, gu.stream())
         assert st == capi.FG_OK, capi.status_str(st)
-        target = (rep + 1) * (N // 128) * ((M + 15) // 16)
+        target = (rep + 1) * (N // 128) * capi.passes(capi.FG_OP_F16_NK, M, N, K)
         assert L.fg_push_wait(flag.data_ptr(), 1, target, ws.ptr, gu.stream()) == capi.FG_OK
         torch.cuda.synchronize()
         assert ws.status() == capi.FG_OK
