@@ -41,7 +41,7 @@ FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only withou
 N_WEIGHT_COPIES = 4
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean over the five launches of one
 # step, from the ncu capture summarised in profiles/bt_sweep__ncu_full.md
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 138.9e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 139.4e6
 
 
 def parse_args():
