@@ -396,7 +396,7 @@ def run_ours(args):
                                                      "unit": "GB/s", "ms_per_step": ms_nccl / args.steps},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "fg::fg_streamk_kernel<1,8|16>",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "fg::fg_streamk_kernel<1,8> (M <= 8), fg::fg_umma_kernel<1,16> (M = 16)",
                      "algorithmic_bytes_per_launch": avg_bytes},
         "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "grouped": grouped,
     }

@@ -105,3 +105,50 @@ class LayerChain:
         if h:
             capi.lib.fg_chain_destroy(h)
             self._handle = None
+
+
+def _main() -> None:
+    """python -m fastgate_b200.chain [--layers 10 --N 8192 --K 8192 --M 16]: per-layer timeline of a
+    stack of dependent square layers (K = N), minimum / median / maximum over the CTAs, in
+    microseconds after the layer's activations became readable for the first CTA."""
+    import argparse
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=10)
+    ap.add_argument("--N", type=int, default=8192)
+    ap.add_argument("--M", type=int, default=16)
+    ap.add_argument("--show", type=int, default=4, help="layers to print (from the fourth on)")
+    a = ap.parse_args()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(1)
+    Ws = [(torch.randn(a.N, a.N, device=dev, generator=g) / a.N ** 0.5).half() for _ in range(a.layers)]
+    bufs = [torch.randn(a.M, a.N, device=dev, generator=g).half()]
+    bufs += [torch.empty(a.M, a.N, dtype=torch.half, device=dev) for _ in range(a.layers)]
+    ch = LayerChain([dict(x=bufs[i], W=Ws[i], C=bufs[i + 1], dep=i - 1) for i in range(a.layers)])
+    for _ in range(3):
+        ch.run()
+    torch.cuda.synchronize()
+    capi.lib.fg_trace_enable(1)
+    try:
+        ch.run()
+        t = ch.trace().double()
+    finally:
+        capi.lib.fg_trace_enable(0)
+    names = ["activations ready", "first stage landed", "last stage committed", "last partial written",
+             "its ticket back", "reduction loaded", "last tile handed on"]
+    cols = [0, 1, 2, 4, 5, 6, 3]
+    first = min(3, a.layers - 1)
+    for layer in range(first, min(a.layers, first + a.show)):
+        t0 = t[layer, :, 0].min()
+        print(f"layer {layer} (starts {float(t0 - t[first, :, 0].min()) / 1e3:.2f} us after layer {first}):")
+        for name, c in zip(names, cols):
+            v = t[layer, :, c]
+            v = (v[v > 0] - t0) / 1e3
+            if len(v):
+                print(f"  {name:22s} min {float(v.min()):6.2f}  med {float(v.median()):6.2f}  max {float(v.max()):6.2f}   ({len(v)} CTAs)")
+    if ch.status() != capi.FG_OK:
+        raise SystemExit("the chain kernel reported a timeout")
+
+
+if __name__ == "__main__":
+    _main()
