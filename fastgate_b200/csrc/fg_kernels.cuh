@@ -684,11 +684,11 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
 }
 
 // Warp roles: [0, ncw) consume, ncw produces (TMA), then two teams of MT/4 warps finish split tiles.
-// The quantized ops are planned with at most four consumer warps (three with a 16-row tile), which
+// The quantized ops are planned with at most six consumer warps (three with a 16-row tile), which
 // keeps the CTA at 384 threads or fewer and leaves their dequantising inner loops 168 registers.
 template <int OP, int MT>
 __host__ __device__ constexpr int streamk_max_threads() {
-  return ((op_is_quantized(OP) ? (MT == 16 ? 3 : 4) : kMaxConsumerWarps) + 1 + 2 * finisher_warps<MT>()) * 32;
+  return ((op_is_quantized(OP) ? (MT == 16 ? 3 : 6) : kMaxConsumerWarps) + 1 + 2 * finisher_warps<MT>()) * 32;
 }
 
 template <int OP, int MT>

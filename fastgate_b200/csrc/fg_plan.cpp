@@ -123,11 +123,12 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
   if (units * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;  // beyond the kernel's 32-bit index math
 
   // Consumer warps, from sweeps on B200: the int8 path is happiest with 3 (its dequantising
-  // inner loop keeps the issue slots busy), fp16 with 4 for an 8-row tile and 8 for 16 rows.
+  // inner loop keeps the issue slots busy), int4 with 5 (28672 x 8192, M = 8: 61 / 55 / 52 / 54.5 us
+  // with 3 / 4 / 5 / 6 warps), fp16 with 4 for an 8-row tile and 8 for 16 rows.
   // A ring stage is always consumed by the same warp (stage s belongs to warp s % warps),
   // which needs stages % warps == 0: a warp then sees every phase of the barriers it waits
   // on.  The ring takes all the shared memory that is left.
-  int warps = (op == FG_OP_W8A16_NK) ? 3 : (op == FG_OP_W4A16_NK) ? (p.m_tile == 16 ? 3 : 4) : (p.m_tile == 16 ? 8 : 4);
+  int warps = (op == FG_OP_W8A16_NK) ? 3 : (op == FG_OP_W4A16_NK) ? (p.m_tile == 16 ? 3 : 5) : (p.m_tile == 16 ? 8 : 4);
   const int stage_bytes = chunks * fg_chunk_bytes(op, p.m_tile);
   int stages = 0;
   for (; warps >= 1; --warps) {
@@ -166,7 +167,7 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   } else {
     if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
     // the dequantising kernels are built for <= 4 consumer warps (<= 3 with a 16-row tile)
-    if (quantized && p->consumer_warps > (p->m_tile == 16 ? 3 : 4)) return FG_ERR_PLAN;
+    if (quantized && p->consumer_warps > (p->m_tile == 16 ? 3 : 6)) return FG_ERR_PLAN;
     // each stage must always meet the same consumer warp (see fg_plan)
     if (p->stages % p->consumer_warps) return FG_ERR_PLAN;
   }

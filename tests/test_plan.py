@@ -79,7 +79,7 @@ def test_plan_invariants(op, M, N, K):
     if p.math == 0:
         assert p.stages % p.consumer_warps == 0, "a ring slot must always meet the same warp"
         if op in (2, 3):  # the dequantising kernels: <= 384 threads per CTA
-            assert p.consumer_warps <= (3 if p.m_tile == 16 else 4)
+            assert p.consumer_warps <= (3 if p.m_tile == 16 else 6)
     else:
         assert p.math == 2 and p.m_tile >= 16, "tcgen05 kernels: accumulator in tensor memory"
         assert p.stages >= 3 or p.k_per_stage == CHUNK_K[op]
