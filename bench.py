@@ -613,7 +613,8 @@ def run_other_workload(args):
                 pbs = [lay.push_buffers(16, dev) for lay in layers]
                 gflag = shard.PushBuffers(16, 128, dev)
                 grp = LinearGroup(g_xs, g_ws, None, peer_C_ptrs=[pb.c_ptrs for pb in pbs], flag_ptrs=gflag.flag_ptrs,
-                                  rank=rank, n_totals=[lay.n_total for lay in layers])
+                                  rank=rank, n_totals=[lay.n_total for lay in layers],
+                                  mc_C_ptrs=[pb.mc_out for pb in pbs], mc_flag_ptr=gflag.mc_flag)
 
                 def step_group():
                     grp.run()

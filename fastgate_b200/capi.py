@@ -43,7 +43,8 @@ class Peers(ctypes.Structure):
 
     _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("n_total", ctypes.c_longlong),
                 ("C", ctypes.c_void_p * 8), ("flag", ctypes.c_void_p * 8),
-                ("wait_flags", ctypes.c_void_p), ("wait_target", ctypes.c_ulonglong)]
+                ("wait_flags", ctypes.c_void_p), ("wait_target", ctypes.c_ulonglong),
+                ("mc_C", ctypes.c_void_p), ("mc_flag", ctypes.c_void_p)]
 
 
 class Epilogue(ctypes.Structure):
@@ -60,7 +61,7 @@ class Problem(ctypes.Structure):
 
     _fields_ = [("x", ctypes.c_void_p), ("W", ctypes.c_void_p), ("C", ctypes.c_void_p),
                 ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
-                ("peer_C", ctypes.c_void_p * 8), ("n_total", ctypes.c_longlong)]
+                ("peer_C", ctypes.c_void_p * 8), ("n_total", ctypes.c_longlong), ("mc_C", ctypes.c_void_p)]
 
 
 class Layer(ctypes.Structure):

@@ -279,7 +279,13 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.wait_flags = nullptr;
   p.wait_world = 0;
   p.wait_target = 0;
+  p.mc_C = nullptr;
+  p.mc_flag = nullptr;
   if (peers != nullptr) {
+    if (peers->mc_C != nullptr && peers->mc_flag != nullptr) {
+      p.mc_C = static_cast<__half*>(peers->mc_C);
+      p.mc_flag = peers->mc_flag;
+    }
     p.wait_flags = peers->wait_flags;
     p.wait_world = peers->world;
     p.wait_target = peers->wait_target;
@@ -305,9 +311,11 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     p.M = mp;
     if (ep != nullptr && ep->residual != nullptr)
       p.residual = static_cast<const __half*>(ep->residual) + static_cast<size_t>(m0) * N;
-    if (peers != nullptr)
+    if (peers != nullptr) {
       for (int q = 0; q < peers->world; ++q)
         p.peer_C[q] = static_cast<__half*>(peers->C[q]) + static_cast<size_t>(m0) * peers->n_total;
+      if (p.mc_C != nullptr) p.mc_C = static_cast<__half*>(peers->mc_C) + static_cast<size_t>(m0) * peers->n_total;
+    }
     if ((st = launch_one(pl, kern, tmW, tmX, p, stream)) != FG_OK) return st;
   }
   return FG_OK;
@@ -459,6 +467,8 @@ int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, 
     if (!aligned16(peers->C[q]) || (reinterpret_cast<uintptr_t>(peers->flag[q]) & 7u) != 0) return FG_ERR_ALIGN;
   }
   if ((reinterpret_cast<uintptr_t>(peers->wait_flags) & 7u) != 0) return FG_ERR_ALIGN;
+  if ((peers->mc_C == nullptr) != (peers->mc_flag == nullptr)) return FG_ERR_NULL;  // both multicast mappings or none
+  if (!aligned16(peers->mc_C) || (reinterpret_cast<uintptr_t>(peers->mc_flag) & 7u) != 0) return FG_ERR_ALIGN;
   int st = check_common(x, W_shard, peers->C[peers->rank], M, N_local, K, ws, ws_bytes);
   if (st != FG_OK) return st;
   DeviceInfo* dev = nullptr;
@@ -495,6 +505,7 @@ struct fg_group {
   int chunks, stages, grid, smem_bytes;
   int world, rank;
   unsigned long long* flag[8];
+  unsigned long long* mc_flag;
 };
 
 size_t fg_group_table_bytes(int count) {
@@ -575,6 +586,7 @@ int fg_group_create(int op, const fg_problem_t* problems, int count, const fg_pe
     if ((st = encode_2d(&en.tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, q.x, q.K, q.M, 64, 16)) != FG_OK) return st;
     en.C = static_cast<__half*>(q.C);
     for (int r = 0; r < world; ++r) en.peer_C[r] = static_cast<__half*>(q.peer_C[r]);
+    en.mc_C = static_cast<__half*>(q.mc_C);
     en.ldc = world ? q.n_total : q.N;
     en.col0 = world ? rank * q.N : 0;
     en.M = q.M;
@@ -607,6 +619,10 @@ int fg_group_create(int op, const fg_problem_t* problems, int count, const fg_pe
   grp->world = world;
   grp->rank = rank;
   for (int q = 0; q < 8; ++q) grp->flag[q] = (q < world) ? peers->flag[q] : nullptr;
+  // multicast only if the flag array and every problem's output have a multicast mapping
+  grp->mc_flag = (world > 0) ? peers->mc_flag : nullptr;
+  for (int i = 0; i < count && grp->mc_flag != nullptr; ++i)
+    if (problems[i].mc_C == nullptr || !aligned16(problems[i].mc_C)) grp->mc_flag = nullptr;
   *out = grp;
   return FG_OK;
 }
@@ -649,6 +665,7 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
   g.world = grp->world;
   g.rank = grp->rank;
   for (int q = 0; q < 8; ++q) g.peer_flag[q] = grp->flag[q];
+  g.mc_flag = grp->mc_flag;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grp->grid);
   cfg.blockDim = dim3(fg::kUmmaGroupThreads);
@@ -1008,6 +1025,10 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   p.bias = nullptr;
   p.residual = nullptr;
   p.act = 0;
+  p.mc_C = nullptr;
+  p.mc_flag = nullptr;
+  p.scale_groups = 1;
+  p.w4_magic = 0;
   p.world = 0;
   p.rank = 0;
   p.col0 = 0;

@@ -104,6 +104,8 @@ struct KParams {
   long long ldc;             // row length of the full output
   __half* peer_C[kMaxPeers];
   unsigned long long* peer_flag[kMaxPeers];
+  __half* mc_C;              // multicast mapping of all ranks' outputs (nullptr: per-peer stores)
+  unsigned long long* mc_flag;  // multicast mapping of all ranks' flag arrays
   // Optional dependency on an earlier pushed layer: the activations are only read once the
   // `wait_world` per-source counters at wait_flags have reached wait_target (nullptr: none).
   const unsigned long long* wait_flags;
@@ -393,6 +395,8 @@ __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float
   const __half2 h = __floats2half2_rn(v.x, v.y);
   if (p.world == 0) {
     *reinterpret_cast<__half2*>(p.C + static_cast<size_t>(m) * p.N + n) = h;
+  } else if (p.mc_C != nullptr) {
+    multimem_st_b32(p.mc_C + static_cast<size_t>(m) * p.ldc + p.col0 + n, *reinterpret_cast<const uint32_t*>(&h));
   } else {
     const size_t off = static_cast<size_t>(m) * p.ldc + p.col0 + n;
     for (int q = 0; q < p.world; ++q) *reinterpret_cast<__half2*>(p.peer_C[q] + off) = h;
@@ -402,6 +406,10 @@ __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float
 // One thread tells every rank that one more output tile of this rank has been delivered.
 // The callers make the tile's stores visible system-wide first (fence + barrier).
 __device__ __forceinline__ void signal_tile_delivered(const KParams& p) {
+  if (p.mc_flag != nullptr) {
+    multimem_red_release_add_u64(p.mc_flag + p.rank, 1ull);
+    return;
+  }
   for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.rank, 1ull);
 }
 

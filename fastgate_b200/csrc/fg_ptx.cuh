@@ -56,6 +56,14 @@ __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity
       : "memory");
   return ok;
 }
+// Multicast ("multimem") store / reduction: one instruction, delivered by the NVSwitch to the
+// copy of the address in every GPU of the multicast group.
+__device__ __forceinline__ void multimem_st_b32(void* mc_ptr, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_red_release_add_u64(unsigned long long* mc_ptr, unsigned long long v) {
+  asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(mc_ptr), "l"(v) : "memory");
+}
 // Release/acquire fence at GPU scope (__threadfence() is the sequentially consistent one).
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 __device__ __forceinline__ uint32_t smid() {

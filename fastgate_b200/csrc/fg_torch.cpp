@@ -159,7 +159,8 @@ void op_wfirst_int4(at::Tensor W4, at::Tensor x, at::Tensor C, c10::optional<at:
 // device addresses, as mapped into this process, of every rank's full output [M, n_total]
 // and arrival counter (e.g. buffer_ptrs of a torch symmetric-memory allocation).
 void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std::vector<int64_t> flag_ptrs,
-                    int64_t rank, int64_t n_total, int64_t wait_flag_ptr, int64_t wait_target) {
+                    int64_t rank, int64_t n_total, int64_t wait_flag_ptr, int64_t wait_target, int64_t mc_c_ptr,
+                    int64_t mc_flag_ptr) {
   check_tensor(x, "activation", at::kHalf);
   check_tensor(W, "weight", at::kHalf);
   if (x.dim() != 2 || W.dim() != 2 || x.size(1) != W.size(1))
@@ -175,6 +176,8 @@ void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std
   peers.n_total = n_total;
   peers.wait_flags = reinterpret_cast<const unsigned long long*>(wait_flag_ptr);
   peers.wait_target = static_cast<unsigned long long>(wait_target);
+  peers.mc_C = reinterpret_cast<void*>(mc_c_ptr);                       // multicast mappings, 0 = none
+  peers.mc_flag = reinterpret_cast<unsigned long long*>(mc_flag_ptr);
   for (size_t q = 0; q < c_ptrs.size(); ++q) {
     peers.C[q] = reinterpret_cast<void*>(c_ptrs[q]);
     peers.flag[q] = reinterpret_cast<unsigned long long*>(flag_ptrs[q]);
@@ -345,7 +348,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("hgemm", &hgemm);
   m.def("hgemm_tr", &hgemm_tr);
   m.def("linear_nk_push", &linear_nk_push, py::arg("x"), py::arg("W"), py::arg("c_ptrs"), py::arg("flag_ptrs"),
-        py::arg("rank"), py::arg("n_total"), py::arg("wait_flag_ptr") = 0, py::arg("wait_target") = 0);
+        py::arg("rank"), py::arg("n_total"), py::arg("wait_flag_ptr") = 0, py::arg("wait_target") = 0,
+        py::arg("mc_c_ptr") = 0, py::arg("mc_flag_ptr") = 0);
   m.def("push_wait", &push_wait, py::arg("flag_ptr"), py::arg("world"), py::arg("target"), py::arg("device"));
   m.def("workspace_status", &workspace_status, py::arg("device"));
   m.def("linear_fused", &linear_fused, py::arg("x"), py::arg("W"), py::arg("C"), py::arg("scales") = py::none(),

@@ -102,6 +102,13 @@ __device__ __forceinline__ void store_out1(const KParams& p, int m, int n, float
   const __half h = __float2half_rn(v);
   if (p.world == 0) {
     p.C[static_cast<size_t>(m) * p.N + n] = h;
+  } else if (p.mc_C != nullptr) {
+    // multicast stores are at least 32 bits wide: even lanes store their column and the next one
+    // (called by whole warps with a uniform m: lane = column within the tile)
+    const unsigned short mine = __half_as_ushort(h);
+    const unsigned int next = __shfl_down_sync(0xffffffffu, static_cast<unsigned int>(mine), 1);
+    if ((n & 1) == 0)
+      multimem_st_b32(p.mc_C + static_cast<size_t>(m) * p.ldc + p.col0 + n, static_cast<uint32_t>(mine) | (next << 16));
   } else {
     const size_t off = static_cast<size_t>(m) * p.ldc + p.col0 + n;
     for (int q = 0; q < p.world; ++q) p.peer_C[q][off] = h;

@@ -21,6 +21,7 @@ struct alignas(128) GroupEntry {
   CUtensorMap tmX;            // activations [M, K], box of 16 rows
   __half* C;                  // local output [M, N]            (world == 0)
   __half* peer_C[kMaxPeers];  // full outputs [M, ldc] of every rank (world > 0)
+  __half* mc_C;               // multicast mapping of those outputs, or nullptr
   long long ldc;
   int col0;                   // first column of this rank's slice in the full output
   int M, N, K;
@@ -43,6 +44,7 @@ struct GParams {
   int world;                  // 0: local outputs
   int rank;
   unsigned long long* peer_flag[kMaxPeers];
+  unsigned long long* mc_flag;  // multicast mapping of the flag arrays: tiles go out by multimem.st / multimem.red
 };
 
 // Position of one stage of the concatenated list.
@@ -89,6 +91,12 @@ __device__ __forceinline__ void group_store1(const GParams& g, const GroupEntry*
   const __half h = __float2half_rn(v);
   if (g.world == 0) {
     e->C[static_cast<size_t>(m) * e->N + n] = h;
+  } else if (g.mc_flag != nullptr) {
+    // multicast stores are at least 32 bits wide: even lanes store their column and the next one
+    const unsigned int mine = __half_as_ushort(h);
+    const unsigned int next = __shfl_down_sync(0xffffffffu, mine, 1);
+    if ((n & 1) == 0)
+      multimem_st_b32(e->mc_C + static_cast<size_t>(m) * e->ldc + e->col0 + n, mine | (next << 16));
   } else {
     const size_t off = static_cast<size_t>(m) * e->ldc + e->col0 + n;
     for (int q = 0; q < g.world; ++q) e->peer_C[q][off] = h;
@@ -98,12 +106,18 @@ __device__ __forceinline__ void group_store2(const GParams& g, const GroupEntry*
   const __half2 h = __floats2half2_rn(v.x, v.y);
   if (g.world == 0) {
     *reinterpret_cast<__half2*>(e->C + static_cast<size_t>(m) * e->N + n) = h;
+  } else if (g.mc_flag != nullptr) {
+    multimem_st_b32(e->mc_C + static_cast<size_t>(m) * e->ldc + e->col0 + n, *reinterpret_cast<const uint32_t*>(&h));
   } else {
     const size_t off = static_cast<size_t>(m) * e->ldc + e->col0 + n;
     for (int q = 0; q < g.world; ++q) *reinterpret_cast<__half2*>(e->peer_C[q] + off) = h;
   }
 }
 __device__ __forceinline__ void group_signal(const GParams& g) {
+  if (g.mc_flag != nullptr) {
+    multimem_red_release_add_u64(g.mc_flag + g.rank, 1ull);
+    return;
+  }
   for (int q = 0; q < g.world; ++q) atomicAdd_system(g.peer_flag[q] + g.rank, 1ull);
 }
 

@@ -20,7 +20,8 @@ from . import capi
 class LinearGroup:
     def __init__(self, xs: Sequence[torch.Tensor], Ws: Sequence[torch.Tensor], Cs: Optional[Sequence[torch.Tensor]],
                  weight_layout: str = "nk", peer_C_ptrs: Optional[Sequence[Sequence[int]]] = None,
-                 flag_ptrs: Optional[Sequence[int]] = None, rank: int = 0, n_totals: Optional[Sequence[int]] = None):
+                 flag_ptrs: Optional[Sequence[int]] = None, rank: int = 0, n_totals: Optional[Sequence[int]] = None,
+                 mc_C_ptrs: Optional[Sequence[int]] = None, mc_flag_ptr: int = 0):
         assert weight_layout in ("nk", "kn")
         n = len(xs)
         assert n == len(Ws) and n > 0
@@ -45,12 +46,16 @@ class LinearGroup:
                 for r, ptr in enumerate(peer_C_ptrs[i]):
                     probs[i].peer_C[r] = ptr
                 probs[i].n_total = n_totals[i]
+                if mc_C_ptrs is not None and mc_C_ptrs[i]:
+                    probs[i].mc_C = mc_C_ptrs[i]  # multicast mapping of the same outputs
         peers = None
         if peer_C_ptrs is not None:
             peers = capi.Peers()
             peers.world, peers.rank = len(flag_ptrs), rank
             for r, ptr in enumerate(flag_ptrs):
                 peers.flag[r] = ptr
+            if mc_flag_ptr and mc_C_ptrs is not None:
+                peers.mc_flag = mc_flag_ptr
         L = capi.lib
         self._table = torch.empty(int(L.fg_group_table_bytes(n)), dtype=torch.uint8, device=self.device)
         handle = ctypes.c_void_p()

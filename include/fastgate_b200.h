@@ -186,6 +186,13 @@ typedef struct fg_peers_t {
    * NULL = x is ready when the call is enqueued. */
   const unsigned long long* wait_flags;
   unsigned long long wait_target;
+  /* Optional: multicast mappings of the same two allocations (an NVLink multicast object bound
+   * to every rank's output / flag array, e.g. the multicast_ptr of a torch symmetric-memory
+   * handle).  When both are set, a finished tile is stored ONCE with multimem.st and signalled
+   * with one multimem.red; the NVSwitch replicates them to all ranks (this one included), which
+   * divides the NVLink egress of the push by world.  NULL = one store and one atomic per rank. */
+  void* mc_C;
+  unsigned long long* mc_flag;
 } fg_peers_t;
 
 int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, int K,
@@ -216,6 +223,8 @@ typedef struct fg_problem_t {
   int M, N, K;
   void* peer_C[8];     /* pushing: full output [M, n_total] of every rank, as mapped here */
   long long n_total;   /* pushing: world * N */
+  void* mc_C;          /* pushing: multicast mapping of the same outputs, or NULL (used only when
+                          peers->mc_flag is set and every problem of the group has one) */
 } fg_problem_t;
 typedef struct fg_group fg_group_t;
 
