@@ -432,8 +432,7 @@ int fg_gemm_w4a16_nk(const void* x, const uint8_t* W4, const void* scales, int g
     DeviceInfo* dev = nullptr;
     if ((st = device_info(&dev)) != FG_OK) return st;
     fg_plan_t pl;
-    // one fp32 scaling per 128-k group: the mma.sync kernel (the tcgen05 one scales per channel only)
-    if ((st = fg_plan_mma_sync(FG_OP_W4A16_NK, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+    if ((st = fg_plan(FG_OP_W4A16_NK, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
     return run_planned(pl, dev, x, W4, scales, C, M, N, K, ws, reinterpret_cast<cudaStream_t>(stream), nullptr,
                        nullptr, &qa);
   }

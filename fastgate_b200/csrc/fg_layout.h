@@ -55,5 +55,5 @@ static inline int fg_umma_smem_bytes(int op, int chunks, int stages) {
 /* token rows one launch covers: 64 for the fp16 tcgen05 kernel, 16 otherwise */
 static inline int fg_pass_rows(int op, int math) { return (math == 2 && op <= 1) ? FG_MAX_M_TILE : 16; }
 static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages) {
-  return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + FG_UMMA_Q_STAGING_BYTES + 128;
+  return 1024 + stages * (chunks * fg_chunk_bytes(op, 16) + 16) + FG_UMMA_Q_STAGING_BYTES + 160;
 }

@@ -93,8 +93,7 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
     // Quantized weights, more than 8 token rows: warps dequantise landed stages into fp16 staging
     // tiles for tcgen05.mma (fg_umma_q_kernel).  Measured on B200 at 28672 x 8192, M = 16: int8
     // 66 us against 70 us for the 16-row mma.sync kernel, int4 58 us against 86 us.  Up to 8 rows
-    // the mma.sync kernel is as fast or faster (int8 follows HBM there).  Group-wise int4 scales
-    // need fp32 scaling per group, which only the mma.sync kernel does: its caller asks for it.
+    // the mma.sync kernel is as fast or faster (int8 follows HBM there).
     p.math = 2;
     p.m_tile = 16;
     p.consumer_warps = 4;
@@ -105,7 +104,7 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
     p.grid = static_cast<int>(std::min<long long>(std::min(sm_count, FG_MAX_GRID), units));
     if (units * p.grid >= (1LL << 31)) return FG_ERR_SHAPE;
     const int stage_bytes = chunks * fg_chunk_bytes(op, 16);
-    p.stages = std::min((smem_optin_bytes - 1024 - 128 - FG_UMMA_Q_STAGING_BYTES) / (stage_bytes + 16), FG_MAX_STAGES);
+    p.stages = std::min((smem_optin_bytes - 1024 - 160 - FG_UMMA_Q_STAGING_BYTES) / (stage_bytes + 16), FG_MAX_STAGES);
     if (p.stages < 2) return FG_ERR_PLAN;
     p.pdl = 1;
     p.smem_bytes = fg_umma_q_smem_bytes(op, chunks, p.stages);

@@ -12,12 +12,14 @@
 // stream (half the bytes of int8 per weight) within what the tensor-core-free part of an SM
 // can convert, where the mma.sync kernel is bound by its fragment traffic and MMA issue.
 //
-//   staging buffer = 128 k:  int8: one 16 KB chunk of the ring;  int4: half a chunk.
-//   Scales are per output channel and stay in the fp32 epilogue, as in the other kernels.  The
-//   kernel can also fold group-wise int4 scales into the dequantisation (one fp16 multiply per
-//   weight), but that rounding costs about 1e-2 absolute at K of a few thousand, which is the
-//   whole tolerance of the path for outputs near zero: the host sends group-wise calls to the
-//   mma.sync kernel, which scales each group's fp32 partial sum instead.
+//   staging buffer = 128 k:  int8: one 16 KB chunk of the ring;  int4: half a chunk, i.e. exactly
+//   one 128-k scale group.  Per-channel scales are applied in the fp32 epilogue as in the other
+//   kernels.  Group-wise int4 scales ("group mode"): every staging buffer is accumulated into a
+//   TMEM tile of its own (the MMA overwrites instead of accumulating), the epilogue warps read it
+//   back as soon as it is complete and add it, times the group's scale, to fp32 sums they keep in
+//   registers.  (Folding the scale into the dequantisation, one fp16 multiply per weight, was
+//   measured at about 1e-2 absolute error for K of a few thousand: the whole tolerance of the
+//   path for outputs near zero.)
 //
 // Warp roles: 0-3 epilogue, 4 producer (TMA), 5 MMA issue and TMEM allocation, 6-9 finishers
 // (the four warps serve both of a CTA's partial tiles, one after the other), 10-17 dequantise,
@@ -34,6 +36,8 @@ constexpr int kUmmaQIssuers = 2;  // MMA-issuing threads, one accumulation chain
 constexpr int kUmmaQThreads = (6 + kUmmaMT / 4 + kUmmaQDequantWarps + (kUmmaQIssuers - 1)) * 32;  // 608
 constexpr uint32_t kStagingBytes = 32768;  // fp16 [128 n][128 k]: two K-major sub-tiles of 16 KB
 constexpr int kNStaging = FG_UMMA_Q_STAGING_BYTES / 32768;  // staging buffers in flight between the dequantisers and the MMA thread
+constexpr uint32_t kTmemColsQ = 128;  // kNStaging accumulator tiles of 2 chains x 16 columns (group mode), rounded up
+static_assert(kNStaging * kUmmaChains * kUmmaMT <= 128, "group mode keeps one accumulator tile per staging buffer");
 
 __device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
@@ -79,15 +83,16 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
   const uint32_t bar_acc_empty = bar_acc_full + 16;             // [2] epilogue -> MMA
   const uint32_t bar_flush = bar_acc_empty + 16;                // [2] epilogue -> finishers (per partial)
   const uint32_t bar_a_full = bar_flush + 16;                   // [kNStaging] dequantisers -> MMA
-  const uint32_t bar_a_empty = bar_a_full + 8 * kNStaging;      // [kNStaging] MMA -> dequantisers
-  const uint32_t tmem_slot = bar_a_empty + 8 * kNStaging;
+  const uint32_t bar_a_empty = bar_a_full + 8 * kNStaging;      // [kNStaging] MMA -> dequantisers (and, in group mode, -> epilogue)
+  const uint32_t bar_g_empty = bar_a_empty + 8 * kNStaging;     // [kNStaging] group mode: epilogue -> MMA (accumulator tile read back)
+  const uint32_t tmem_slot = bar_g_empty + 8 * kNStaging;
   const uint32_t tail = ring_bytes + kNStaging * kStagingBytes + 16 * S;
-  constexpr uint32_t kBarBytes = 48 + 16 * kNStaging;           // the barriers after full[] / empty[]
+  constexpr uint32_t kBarBytes = 48 + 24 * kNStaging;           // the barriers after full[] / empty[]
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + kBarBytes);
   volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + tail + kBarBytes + 4);  // [2]
-  static_assert(kBarBytes + 16 <= 128, "barrier block outgrew its reservation (fg_umma_q_smem_bytes)");
+  static_assert(kBarBytes + 16 <= 160, "barrier block outgrew its reservation (fg_umma_q_smem_bytes)");
 
-  if (blockDim.x != static_cast<unsigned>(kUmmaQThreads) || dynamic_smem_size() < 1023u + tail + 128u) {
+  if (blockDim.x != static_cast<unsigned>(kUmmaQThreads) || dynamic_smem_size() < 1023u + tail + 160u) {
     if (threadIdx.x == 0) atomicExch(p.status, kStatusBadLaunch);
     return;
   }
@@ -113,12 +118,13 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
     for (int b = 0; b < kNStaging; ++b) {
       mbar_init(bar_a_full + 8 * b, kUmmaQDequantWarps * 32);
       mbar_init(bar_a_empty + 8 * b, kUmmaQIssuers);
+      mbar_init(bar_g_empty + 8 * b, 4);
     }
     fence_mbar_init();
     fence_proxy_async();
   }
   if (warp == 5) {
-    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_alloc(tmem_slot, kTmemColsQ);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -132,6 +138,7 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
   const CtaRange range{KB, total, G, range_begin(blockIdx.x, total, G), range_begin(blockIdx.x + 1, total, G)};
   const uint32_t ub = range.ub, ue = range.ue;
   const int k_per_stage = cps * T::chunkK;
+  const bool gmode = (OP == kOpW4A16NK) && p.scale_groups > 1;  // one accumulator tile per 128-k group
 
   if (warp == 4) {
     if (lane == 0) run_producer<OP, MT>(tmW, tmX, p, range, smem_base, bar_base, S, cps, trace);
@@ -152,7 +159,6 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
     const int d = threadIdx.x - 10 * 32;
     const int row = d & 127, khalf = d >> 7;
     const uint32_t sw = static_cast<uint32_t>(row & 7);
-    const bool grouped = (OP == kOpW4A16NK) && p.scale_groups > 1;
     uint32_t u = ub;
     int s = 0;
     uint32_t ph = 0;
@@ -166,18 +172,6 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
         const int k0 = (kb0 + it) * k_per_stage;
         int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
         nch = nch < cps ? nch : cps;
-        // group scales of this row for the whole stage, requested before the stage is waited for
-        __half gs[4 * kHalves];
-        if (grouped) {
-#pragma unroll
-          for (int i = 0; i < 4 * kHalves; ++i) {
-            int gi = (k0 >> 7) + i;
-            gi = gi < p.scale_groups ? gi : p.scale_groups - 1;
-            gs[i] = (i < nch * kHalves)
-                        ? __ldg(p.scales + static_cast<size_t>(tile * kTileN + row) * p.scale_groups + gi)
-                        : __half(0.f);
-          }
-        }
         if (!mbar_wait_bounded(bar_base + 8 * s, ph, kWaitBudgetNs * 2)) {
           dead = true;
           break;
@@ -194,11 +188,6 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
             }
             const uint32_t dst_row = staging + buf * kStagingBytes + khalf * 16384 + row * 128;
             if constexpr (OP == kOpW4A16NK) {
-              uint32_t sc2 = 0;
-              if (grouped) {
-                const __half2 h2 = __half2half2(gs[c * kHalves + hf]);
-                sc2 = *reinterpret_cast<const uint32_t*>(&h2);
-              }
 #pragma unroll
               for (int pc = 0; pc < 2; ++pc) {
                 const uint32_t piece = hf * 4 + khalf * 2 + pc;
@@ -208,10 +197,6 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
                 for (int wi = 0; wi < 4; ++wi) {
                   uint32_t o[4];
                   dequant_u4x8_ordered(w[wi], p.w4_magic, o);
-                  if (grouped) {
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) o[i] = hmul2_u32(o[i], sc2);
-                  }
                   sts_v4(dst_row + (((pc * 4 + wi) ^ sw) << 4), o[0], o[1], o[2], o[3]);
                 }
               }
@@ -263,12 +248,12 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
         const int kb0 = static_cast<int>(u - tile * KB);
         const int len = static_cast<int>((KB - kb0) < (ue - u) ? (KB - kb0) : (ue - u));
         const uint32_t b = sg & 1, use = sg >> 1;
-        if (!mbar_wait_bounded(bar_acc_empty + 8 * b, (use & 1) ^ 1, kWaitBudgetNs * 2)) {
+        if (!gmode && !mbar_wait_bounded(bar_acc_empty + 8 * b, (use & 1) ^ 1, kWaitBudgetNs * 2)) {
           dead = true;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT) + iss * kUmmaMT;
+        uint32_t tmem_d = tmem_base + b * (kUmmaChains * kUmmaMT) + iss * kUmmaMT;
         uint32_t acc_flag = 0;
         for (int it = 0; it < len && !dead; ++it, s = (s + 1 == S) ? 0 : s + 1) {
           const int k0 = (kb0 + it) * k_per_stage;
@@ -284,6 +269,15 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
               if (!mbar_wait_bounded(bar_a_full + 8 * buf, bph, kWaitBudgetNs * 2)) {
                 dead = true;
                 break;
+              }
+              if (gmode) {
+                // this group's accumulator tile: free once the epilogue has read its previous content
+                if (!mbar_wait_bounded(bar_g_empty + 8 * buf, bph ^ 1, kWaitBudgetNs * 2)) {
+                  dead = true;
+                  break;
+                }
+                tmem_d = tmem_base + buf * (kUmmaChains * kUmmaMT) + iss * kUmmaMT;
+                acc_flag = 0;
               }
               tc_fence_after_sync();
               const uint32_t ab = staging + buf * kStagingBytes;
@@ -306,7 +300,7 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
           umma_commit(bar_base + 8 * (S + s));  // the ring slot is free once these MMAs have read its activations
         }
         if (dead) break;
-        umma_commit(bar_acc_full + 8 * b);
+        if (!gmode) umma_commit(bar_acc_full + 8 * b);
         if (trace && iss == 0) trace[4] = globaltimer_ns();
         ++sg;
         u += len;
@@ -320,6 +314,7 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
     const int n_in_tile = warp * 32 + lane;
     uint32_t u = ub;
     uint32_t sg = 0, ev = 0;
+    uint32_t buf = 0, bph = 0;  // group mode: accumulator tile in turn (= staging buffer) and its parity
     bool dead = false;
     while (u < ue) {
       const uint32_t tile = u / KB;
@@ -330,7 +325,57 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
       uint32_t r[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) r[i] = 0;
-      if (!dead) {
+      if (gmode) {
+        // one accumulator tile per 128-k group: read each back as it completes and add it, times
+        // the group's scale, to the running fp32 sums of this thread's output column
+        float acc[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] = 0.f;
+        const __half* srow = p.scales + static_cast<size_t>(tile * kTileN + n_in_tile) * p.scale_groups;
+        for (uint32_t it = 0; it < len; ++it) {
+          const int k0 = static_cast<int>(kb0 + it) * k_per_stage;
+          int nch = (p.K - k0 + T::chunkK - 1) / T::chunkK;
+          nch = nch < cps ? nch : cps;
+          const int ngroups = nch * kHalves;
+          __half gs[4 * kHalves];  // the stage's scales, requested before its first tile is waited for
+#pragma unroll
+          for (int i = 0; i < 4 * kHalves; ++i) {
+            int gi = (k0 >> 7) + i;
+            gi = gi < p.scale_groups ? gi : p.scale_groups - 1;
+            gs[i] = (i < ngroups) ? __ldg(srow + gi) : __half(0.f);
+          }
+#pragma unroll
+          for (int i = 0; i < 4 * kHalves; ++i) {
+            if (i >= ngroups) break;
+            if (!dead) {
+              bool ok = mbar_wait_bounded(bar_a_empty + 8 * buf, bph, kWaitBudgetNs * 4);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) {
+                dead = true;
+                if (lane == 0) atomicExch(p.status, kStatusTimeout);
+              }
+            }
+            if (!dead) {
+              uint32_t q[32];
+              tc_fence_after_sync();
+              tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + buf * (kUmmaChains * kUmmaMT), q);
+              tmem_ld_wait();
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_g_empty + 8 * buf);
+              const float sc = __half2float(gs[i]);
+#pragma unroll
+              for (int m = 0; m < MT; ++m) acc[m] += (__uint_as_float(q[m]) + __uint_as_float(q[MT + m])) * sc;
+            }
+            if (++buf == kNStaging) {
+              buf = 0;
+              bph ^= 1;
+            }
+          }
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) r[m] = __float_as_uint(acc[m]);
+      } else if (!dead) {
         bool ok = mbar_wait_bounded(bar_acc_full + 8 * b, use & 1, kWaitBudgetNs * 4);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
@@ -338,7 +383,7 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
           if (lane == 0) atomicExch(p.status, kStatusTimeout);
         }
       }
-      if (!dead) {
+      if (!gmode && !dead) {
         tc_fence_after_sync();
         tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + b * (kUmmaChains * kUmmaMT), r);
         tmem_ld_wait();
@@ -374,7 +419,7 @@ __global__ void __launch_bounds__(kUmmaQThreads, 1)
   named_bar_sync(2, 160);
   if (warp == 5) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, kTmemColsQ);
   }
 }
 
