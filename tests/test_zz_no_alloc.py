@@ -49,6 +49,23 @@ def test_noalloc_matches_workspace_entry_point_twice(M, N, K):
         oracle.check_tolerance(got.cpu().numpy(), oracle.gemm_nk(x.cpu().numpy(), W.cpu().numpy()), "oracle")
 
 
+def test_noalloc_more_than_16_rows_runs_in_16_row_passes():
+    """The built-in scratch holds 16-row partial tiles, so a taller call goes in passes of 16
+    (the workspace entry point would take 64 rows at once): same values within one rounding step."""
+    assert torch.cuda.is_available(), "needs a B200"
+    dev = torch.device("cuda:0")
+    M, N, K = 40, 4096, 4096
+    case = wl.Case("noalloc_tall", wl.OP_NK, M, N, K, 8810)
+    x, W = wl.make_activation(case).to(dev), wl.make_weight(case).to(dev)
+    got = torch.full((M, N), float("nan"), dtype=torch.float16, device=dev)
+    n0 = capi.launch_count()
+    st = capi.lib.fg_gemm_f16_nk_noalloc(x.data_ptr(), W.data_ptr(), got.data_ptr(), M, N, K, _stream())
+    assert st == capi.FG_OK, capi.status_str(st)
+    torch.cuda.synchronize()
+    assert capi.launch_count() - n0 == 3
+    oracle.check_tolerance(got.cpu().numpy(), oracle.gemm_nk(x.cpu().numpy(), W.cpu().numpy()), "tall noalloc")
+
+
 def test_noalloc_rejects_what_does_not_fit():
     assert torch.cuda.is_available(), "needs a B200"
     dev = torch.device("cuda:0")
