@@ -733,7 +733,9 @@ int fg_chain_create(int op, const fg_layer_t* layers, int count, void* table_dev
     if (q.act < FG_ACT_NONE || q.act > FG_ACT_SILU) return FG_ERR_PLAN;
     if (q.dep < -1 || q.dep >= i) return FG_ERR_PLAN;
   }
-  // stage size: as large as still leaves every CTA about six stages per layer on average
+  // stage size: as large as still leaves every CTA about six stages per layer on average.  (Unlike
+  // the single-layer kernel, the chain did not gain from 64 KB stages on the DiT stack: 15.0 us per
+  // layer against 14.7 us with 32 KB stages, which leave the ring six deep across a layer boundary.)
   const int sms = dev->sm_count < FG_MAX_GRID ? dev->sm_count : FG_MAX_GRID;
   int chunks = 4;
   long long units = 0, max_units = 0;

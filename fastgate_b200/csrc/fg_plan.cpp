@@ -54,16 +54,15 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
   if (!quantized && p.m_tile >= 16) {
     // fp16 weights, more than 8 token rows: the tcgen05 kernel (accumulator in tensor memory,
     // no cross-warp reduction, the whole shared memory is ring).  Its single MMA-issuing
-    // thread pays a fixed cost per stage, so stages are as large as the work allows:
-    // measured on B200, 64 KB stages beat 32 KB beat 16 KB as long as a CTA still gets
-    // enough of them to balance the load.
+    // thread pays a fixed cost per stage, so stages are as large as the ring allows: measured
+    // on B200 at M = 16, 64 KB stages (3 in the ring) beat 32 KB (6) beat 16 KB (12) for every
+    // shape tried, from 8192 x 8192 (24.5 / 26.0 / 32.8 us) down to 1024 x 1024 (7.2 / 7.9 / 9.5)
+    // and 9216 x 3072 (13.6 / 16.1 / 19.7), although small layers then get only two or three
+    // stages per CTA.
     p.math = 2;
     p.consumer_warps = 4;  // epilogue warps, fixed
     int chunks = 4;
-    for (; chunks > 1; chunks >>= 1) {
-      const long long kb = (K + chunks * chunk_k - 1) / (chunks * chunk_k);
-      if (static_cast<long long>(p.tiles) * kb >= 6LL * sm_count) break;
-    }
+    while (chunks > 1 && chunks * chunk_k > K) chunks >>= 1;  // a stage never spans more than K
     p.k_per_stage = chunks * chunk_k;
     p.k_blocks = (K + p.k_per_stage - 1) / p.k_per_stage;
     const long long units = static_cast<long long>(p.tiles) * p.k_blocks;
