@@ -51,8 +51,10 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
   p.tiles = N / 128;
 
   const int chunk_k = fg_chunk_k(op);
-  if (!quantized && p.m_tile >= 16) {
-    // fp16 weights, more than 8 token rows: the tcgen05 kernel (accumulator in tensor memory,
+  if (!quantized && (p.m_tile >= 16 || op == FG_OP_F16_NK)) {
+    // NxK fp16 weights at every M, KxN above 8 token rows (measured: with 64 KB stages the tcgen05
+    // kernel is 1.5-5 % faster than the mma.sync one for NxK at M = 1 and 8 on 8192^2, 11008 x 4096,
+    // 4096 x 11008 and 3072^2, and 3 % slower for KxN at 4096^2): the tcgen05 kernel (accumulator in tensor memory,
     // no cross-warp reduction, the whole shared memory is ring).  Its single MMA-issuing
     // thread pays a fixed cost per stage, so stages are as large as the ring allows: measured
     // on B200 at M = 16, 64 KB stages (3 in the ring) beat 32 KB (6) beat 16 KB (12) for every
@@ -60,6 +62,7 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
     // and 9216 x 3072 (13.6 / 16.1 / 19.7), although small layers then get only two or three
     // stages per CTA.
     p.math = 2;
+    if (p.m_tile < 16) p.m_tile = 16;  // rows beyond M are zero-filled by the TMA
     p.consumer_warps = 4;  // epilogue warps, fixed
     int chunks = 4;
     while (chunks > 1 && chunks * chunk_k > K) chunks >>= 1;  // a stage never spans more than K

@@ -214,8 +214,10 @@ def test_linearity_and_row_independence(dev, ws):
 
 
 def test_layouts_agree_bitwise(dev, ws):
-    """KxN and NxK storage of the same weight give the same bits (same summation order),
-    in the tcgen05 kernel (16 rows) and in the mma.sync kernel (8 rows)."""
+    """KxN and NxK storage of the same weight give the same bits in the same kernel (same
+    summation order): the tcgen05 kernel at 16 rows and, with the tcgen05 plan handed to the KxN
+    call, at 8 rows.  The planner's own choice for KxN at 8 rows is the mma.sync kernel, which
+    cuts the sums differently: one rounding step apart."""
     case = wl.Case("kn_vs_nk", wl.OP_NK, 16, 4096, 4096, 99)
     x, W, _ = inputs(case)
     a = torch.zeros(16, 4096, dtype=torch.float16, device=dev)
@@ -226,8 +228,15 @@ def test_layouts_agree_bitwise(dev, ws):
     a8 = torch.zeros(8, 4096, dtype=torch.float16, device=dev)
     b8 = torch.zeros(8, 4096, dtype=torch.float16, device=dev)
     assert gu.call(wl.OP_NK, x[:8].contiguous().to(dev), W.to(dev), None, a8, 8, 4096, 4096, ws) == capi.FG_OK
-    assert gu.call(wl.OP_KN, x[:8].contiguous().to(dev), W.t().contiguous().to(dev), None, b8, 8, 4096, 4096, ws) == capi.FG_OK
+    umma_kn = capi.plan(wl.OP_KN, 16, 4096, 4096, 148, 232448)  # serves any M <= 16
+    assert umma_kn.math == 2
+    assert gu.call(wl.OP_KN, x[:8].contiguous().to(dev), W.t().contiguous().to(dev), None, b8, 8, 4096, 4096, ws,
+                   plan=umma_kn) == capi.FG_OK
     assert torch.equal(a8.view(torch.int16), b8.view(torch.int16))
+    c8 = torch.zeros(8, 4096, dtype=torch.float16, device=dev)
+    assert capi.plan(wl.OP_KN, 8, 4096, 4096, 148, 232448).math == 0
+    assert gu.call(wl.OP_KN, x[:8].contiguous().to(dev), W.t().contiguous().to(dev), None, c8, 8, 4096, 4096, ws) == capi.FG_OK
+    assert _one_rounding_step_apart(c8, a8)
 
 
 def test_n_shards_concatenate_to_the_full_result(dev, ws):
@@ -355,8 +364,9 @@ def test_errors_with_device_present(dev, ws):
     bad.stages += 1
     assert Lc.fg_gemm_planned(ctypes.byref(bad), x.data_ptr(), W.data_ptr(), None, out.data_ptr(), 16, 256, 256,
                               ws.ptr, ws.bytes, gu.stream()) == capi.FG_ERR_PLAN
-    # a plan for 8 rows cannot serve 16
-    p8 = capi.plan(wl.OP_NK, 8, 256, 256, 148, 232448)
+    # a plan for 8 rows (KxN weights: the 8-row mma.sync kernel) cannot serve 16
+    p8 = capi.plan(wl.OP_KN, 8, 256, 256, 148, 232448)
+    assert p8.m_tile == 8
     p8.passes = 1
     assert Lc.fg_gemm_planned(ctypes.byref(p8), x.data_ptr(), W.data_ptr(), None, out.data_ptr(), 16, 256, 256,
                               ws.ptr, ws.bytes, gu.stream()) == capi.FG_ERR_PLAN

@@ -71,6 +71,7 @@ def test_plan_invariants(op, M, N, K):
     p = capi.plan(op, M, N, K, **B200)
     assert p.op == op and p.tiles == N // 128
     assert p.m_tile in (8, 16, 32, 64) and (p.m_tile >= 16 or M <= 8)
+    assert p.m_tile >= min(M, 16)
     assert p.m_tile <= 16 or (op in (0, 1) and p.math == 2), "tall tiles: fp16 tcgen05 kernel only"
     assert p.k_per_stage % CHUNK_K[op] == 0
     assert p.k_blocks == -(-K // p.k_per_stage)
@@ -83,7 +84,8 @@ def test_plan_invariants(op, M, N, K):
     else:
         assert p.math == 2 and p.m_tile >= 16, "tcgen05 kernels: accumulator in tensor memory"
         assert p.stages >= 3 or p.k_per_stage == CHUNK_K[op]
-    assert (p.math == 2) == (M > 8), "more than 8 token rows go to the tcgen05 kernels"
+    # NxK fp16 weights always take the tcgen05 kernel, everything else above 8 token rows
+    assert (p.math == 2) == (M > 8 or op == 1)
     assert p.smem_bytes <= 232448
     rows = 64 if (p.math == 2 and op in (0, 1)) else 16
     assert p.passes == -(-M // rows)
@@ -111,7 +113,7 @@ def test_plan_rejects_bad_problems():
 
 def test_validate_catches_edited_plans():
     L = capi.lib
-    good = capi.plan(1, 8, 8192, 8192, **B200)
+    good = capi.plan(0, 8, 8192, 8192, **B200)  # KxN weights at 8 rows: the mma.sync kernel
     assert good.math == 0
 
     def edited(**kw):
