@@ -43,7 +43,7 @@ FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only withou
 N_WEIGHT_COPIES = 4
 # dram__bytes_read.sum + dram__bytes_write.sum per launch, mean over the five launches of one
 # step, from the ncu capture summarised in profiles/bt_sweep__ncu_full.md
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 139.4e6
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 138.3e6
 
 
 def parse_args():
@@ -479,7 +479,7 @@ def run_ours(args):
                                                      "unit": "GB/s", "ms_per_step": ms_nccl / args.steps},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "fg::fg_streamk_kernel<1,8> (M <= 8), fg::fg_umma_kernel<1,16> (M = 16)",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "kernel": "fg::fg_umma_kernel<1,16>",
                      "algorithmic_bytes_per_launch": avg_bytes},
         "clocks": clocks, "gpu_launches": int(launches), "e2e": e2e, "grouped": grouped,
     }
