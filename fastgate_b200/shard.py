@@ -66,10 +66,10 @@ class PushBuffers:
             # Measured on B200 (DiT stack, one grouped launch per pass, all-gather included): at 2 GPUs
             # the multicast path is 11 % slower than one store per rank (nothing to save on egress, one
             # more hop through the switch), at 8 GPUs 23 % faster (34.6 against 28.3 TB/s); the chained
-            # 8192 x 8192 sweep does not care (26.4 against 26.2 TB/s at 8 GPUs).  Default: from 4 ranks
-            # on; FASTGATE_MULTIMEM=0 / 1 forces it off / on.
+            # 8192 x 8192 sweep does not care (26.4 against 26.2 TB/s at 8 GPUs).  Not measured at 4.
+            # Default: on from 8 ranks; FASTGATE_MULTIMEM=0 / 1 forces it off / on.
             env = os.environ.get("FASTGATE_MULTIMEM")
-            want = (env == "1") if env in ("0", "1") else self.world >= 4
+            want = (env == "1") if env in ("0", "1") else self.world >= 8
             if not (want and self.mc_out and self.mc_flag):
                 self.mc_out = self.mc_flag = 0
             dist.barrier(group)  # every counter is zero before anyone pushes
