@@ -4,9 +4,9 @@
 // from the TMA ring straight into tcgen05.mma as the fp16 ops do.  Eight warps stand in between:
 // they read a landed stage's packed rows, dequantise them in registers and write fp16 tiles in
 // the layout the TMA would have produced for an fp16 weight (K-major [128 n][64 k], rows of
-// 128 B, 128B swizzle) into one of two 32 KB staging buffers, each holding 128 consecutive k of
-// the 128 output columns.  One thread then issues the MMAs against the staging buffer and the
-// activation boxes of the stage, exactly as fg_umma_kernel does.  With fragments and
+// 128 B, 128B swizzle) into one of three 32 KB staging buffers, each holding 128 consecutive k of
+// the 128 output columns.  Two threads (one accumulation chain each) then issue the MMAs against
+// the staging buffer and the activation boxes of the stage, as fg_umma_kernel's one thread does.  With fragments and
 // accumulators out of the register file, dequantisation is the only per-element work left to
 // the SM's issue slots (about 13 instructions per eight int4 weights), which keeps an int4
 // stream (half the bytes of int8 per weight) within what the tensor-core-free part of an SM
