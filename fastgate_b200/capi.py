@@ -32,7 +32,7 @@ class Plan(ctypes.Structure):
 
     _fields_ = [(n, ctypes.c_int) for n in (
         "op", "m_tile", "k_per_stage", "stages", "consumer_warps", "grid", "tiles", "k_blocks",
-        "smem_bytes", "passes", "math", "pdl")]
+        "smem_bytes", "passes", "math", "pdl", "rows_per_stage", "static_rows")]
 
     def as_dict(self) -> dict:
         return {n: getattr(self, n) for n, _ in self._fields_}
@@ -83,6 +83,7 @@ def _load() -> ctypes.CDLL:
     vp, sz, i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
     L.fg_plan.argtypes = [i, i, i, i, i, i, ctypes.POINTER(Plan)]
     L.fg_plan_validate.argtypes = [ctypes.POINTER(Plan), i, i, i]
+    L.fg_plan_tiled.argtypes = [i, i, i, i, i, i, ctypes.POINTER(Plan)]  # internal: never the row-split GEMV plan
     L.fg_workspace_bytes.argtypes = [i]
     L.fg_workspace_bytes.restype = sz
     L.fg_workspace_init.argtypes = [vp, sz, vp]

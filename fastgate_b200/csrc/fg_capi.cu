@@ -14,6 +14,7 @@
 #include "../../include/fastgate_b200.h"
 #include "fg_kernels.cuh"
 #include "fg_umma.cuh"
+#include "fg_gemv.cuh"
 #include "fg_umma_group.cuh"
 #include "fg_umma_chain.cuh"
 #include "fg_umma_q.cuh"
@@ -39,6 +40,12 @@ namespace {
 
 thread_local int g_last_cuda = 0;
 std::atomic<int> g_trace{0};
+// While tracing, consecutive launches of the single-problem kernels write to eight rotating blocks of
+// kTraceBlockCtas CTAs each, so that a launch that overlaps its predecessor (programmatic dependent
+// launch) does not overwrite its stamps; fg_trace_enable restarts the rotation at block 0.
+std::atomic<unsigned int> g_trace_seq{0};
+constexpr int kTraceBlocks = 8;
+constexpr int kTraceBlockCtas = 256;
 // The tracer borrows the partial-tile slots of CTAs 200.. (unused while grid <= 200).
 constexpr int kTraceFirstCta = 200;
 std::atomic<unsigned long long> g_launches{0};
@@ -67,6 +74,7 @@ struct DeviceInfo {
   int cc_major = 0;
   int smem_set[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
   int smem_set_umma[4][3] = {};
+  int smem_set_gemv[FG_GEMV_MAX_M] = {};
   int smem_set_group[2] = {0, 0};
   int smem_set_chain[2] = {0, 0};
 };
@@ -174,9 +182,10 @@ int check_common(const void* x, const void* W, const void* C, int M, int N, int 
 // so a plan can never be launched with another kernel's thread count or memory layout.
 int prepare_kernel(const fg_plan_t& pl, DeviceInfo* dev, KernelFn* out) {
   const bool umma = (pl.math == 2);
+  const int tall = pl.m_tile == 64 ? 2 : pl.m_tile == 32 ? 1 : 0;
   KernelFn kern = umma ? pick_umma_kernel(pl.op, pl.m_tile) : pick_kernel(pl.op, pl.m_tile);
-  int& set = umma ? dev->smem_set_umma[pl.op][pl.m_tile == 64 ? 2 : pl.m_tile == 32 ? 1 : 0]
-                  : dev->smem_set[pl.op][pl.m_tile == 16];
+  std::lock_guard<std::mutex> lk(g_dev_mu);  // the opt-in bookkeeping is shared by all host threads
+  int& set = umma ? dev->smem_set_umma[pl.op][tall] : dev->smem_set[pl.op][pl.m_tile == 16];
   if (pl.smem_bytes > set) {
     const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
@@ -215,6 +224,74 @@ int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const
   return FG_OK;
 }
 
+// ---- row-split GEMV kernel (plan.math == 4) -------------------------------------------------
+using GemvFn = void (*)(const fg::GemvParams);
+
+GemvFn pick_gemv_kernel(int M) { return M == 1 ? fg::fg_gemv_kernel<1> : fg::fg_gemv_kernel<2>; }
+
+int run_gemv(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W, const void* scales, void* C, int M,
+             int N, int K, void* ws, cudaStream_t stream, const fg_epilogue_t* ep) {
+  if (M != pl.m_tile || M < 1 || M > FG_GEMV_MAX_M) return FG_ERR_PLAN;
+  if (pl.op != FG_OP_F16_NK) return FG_ERR_PLAN;
+  GemvFn kern = pick_gemv_kernel(M);
+  {
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    int& set = dev->smem_set_gemv[M - 1];
+    if (pl.smem_bytes > set) {
+      const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
+      if (e != cudaSuccess) {
+        g_last_cuda = static_cast<int>(e);
+        return FG_ERR_CUDA;
+      }
+      set = pl.smem_bytes;
+    }
+  }
+  uint8_t* wsb = static_cast<uint8_t*>(ws);
+  fg::GemvParams p;
+  p.W = W;
+  p.x = static_cast<const __half*>(x);
+  p.C = static_cast<__half*>(C);
+  (void)scales;
+  p.bias = ep ? static_cast<const __half*>(ep->bias) : nullptr;
+  p.residual = ep ? static_cast<const __half*>(ep->residual) : nullptr;
+  p.act = ep ? ep->act : 0;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.rows_per_stage = pl.rows_per_stage;
+  p.stage_bytes = pl.rows_per_stage * K * 2;
+  p.stages = pl.stages;
+  p.static_rows = pl.static_rows;
+  p.l2_prefetch_bytes = pl.pdl ? FG_GEMV_L2_PREFETCH_BYTES : 0;
+  p.next = reinterpret_cast<unsigned int*>(wsb + FG_WS_GEMV_NEXT_OFFSET);
+  p.exited = reinterpret_cast<unsigned int*>(wsb + FG_WS_GEMV_EXITED_OFFSET);
+  p.status = reinterpret_cast<int*>(wsb);
+  p.trace = nullptr;
+  if (g_trace.load(std::memory_order_relaxed) && pl.grid <= kTraceFirstCta)
+    p.trace = reinterpret_cast<unsigned long long*>(wsb + FG_WS_HEADER_BYTES +
+                                                    static_cast<size_t>(kTraceFirstCta) * 2 * FG_WS_PARTIAL_TILE_BYTES) +
+              static_cast<size_t>(g_trace_seq.fetch_add(1, std::memory_order_relaxed) % kTraceBlocks) * kTraceBlockCtas *
+                  fg::kTraceSlots;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.grid);
+  cfg.blockDim = dim3((pl.consumer_warps + 1) * 32);
+  cfg.dynamicSmemBytes = pl.smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pl.pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
 // int4 op: scales per row and the zero point
 struct QuantArgs {
   int groups;
@@ -226,6 +303,10 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
                 const fg_peers_t* peers = nullptr, const fg_epilogue_t* ep = nullptr,
                 const QuantArgs* qa = nullptr) {
   const int op = pl.op;
+  if (pl.math == 4) {
+    if (peers != nullptr || qa != nullptr) return FG_ERR_PLAN;  // the row-split kernel neither pushes nor takes int4
+    return run_gemv(pl, dev, x, W, scales, C, M, N, K, ws, stream, ep);
+  }
   const int chunks = pl.k_per_stage / fg_chunk_k(op);
   KernelFn kern = nullptr;
   {
@@ -259,7 +340,9 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.trace = nullptr;
   if (g_trace.load(std::memory_order_relaxed) && pl.grid <= kTraceFirstCta)
     p.trace = reinterpret_cast<unsigned long long*>(wsb + FG_WS_HEADER_BYTES +
-                                                    static_cast<size_t>(kTraceFirstCta) * 2 * FG_WS_PARTIAL_TILE_BYTES);
+                                                    static_cast<size_t>(kTraceFirstCta) * 2 * FG_WS_PARTIAL_TILE_BYTES) +
+              static_cast<size_t>(g_trace_seq.fetch_add(1, std::memory_order_relaxed) % kTraceBlocks) * kTraceBlockCtas *
+                  fg::kTraceSlots;
   p.N = N;
   p.K = K;
   p.tiles = pl.tiles;
@@ -447,6 +530,7 @@ int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const v
   DeviceInfo* dev = nullptr;
   if ((st = device_info(&dev)) != FG_OK) return st;
   if ((st = fg_plan_validate(plan, N, K, dev->smem_optin)) != FG_OK) return st;
+  if (plan->op == FG_OP_W4A16_NK) return FG_ERR_PLAN;  // needs groups and zero point: fg_gemm_w4a16_nk
   {
     const int rows = fg_pass_rows(plan->op, plan->math);
     if (plan->passes != (M + rows - 1) / rows) return FG_ERR_PLAN;
@@ -473,7 +557,7 @@ int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, 
   DeviceInfo* dev = nullptr;
   if ((st = device_info(&dev)) != FG_OK) return st;
   fg_plan_t pl;
-  if ((st = fg_plan(FG_OP_F16_NK, M, N_local, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+  if ((st = fg_plan_tiled(FG_OP_F16_NK, M, N_local, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
   return run_planned(pl, dev, x, W_shard, nullptr, peers->C[peers->rank], M, N_local, K, ws,
                      reinterpret_cast<cudaStream_t>(stream), peers);
 }
@@ -637,6 +721,7 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
   if (cudaGetDevice(&dev_index) != cudaSuccess || dev_index != grp->device) return FG_ERR_NO_DEVICE;
   using GroupFn = void (*)(const fg::GParams);
   GroupFn kern = grp->op == FG_OP_F16_KN ? fg::fg_umma_group_kernel<fg::kOpF16KN> : fg::fg_umma_group_kernel<fg::kOpF16NK>;
+  std::unique_lock<std::mutex> lk(g_dev_mu);
   int& set = dev->smem_set_group[grp->op == FG_OP_F16_NK];
   if (grp->smem_bytes > set) {
     const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
@@ -647,6 +732,7 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
     }
     set = grp->smem_bytes;
   }
+  lk.unlock();
   uint8_t* wsb = static_cast<uint8_t*>(ws);
   fg::GParams g;
   g.table = grp->table_dev;
@@ -821,6 +907,7 @@ int fg_chain_run(const fg_chain_t* ch, void* ws, size_t ws_bytes, fg_stream_t st
   if (cudaGetDevice(&dev_index) != cudaSuccess || dev_index != ch->device) return FG_ERR_NO_DEVICE;
   using ChainFn = void (*)(const fg::CParams);
   ChainFn kern = ch->op == FG_OP_F16_KN ? fg::fg_umma_chain_kernel<fg::kOpF16KN> : fg::fg_umma_chain_kernel<fg::kOpF16NK>;
+  std::unique_lock<std::mutex> lk(g_dev_mu);
   int& set = dev->smem_set_chain[ch->op == FG_OP_F16_NK];
   cudaError_t e;
   if (ch->smem_bytes > set) {
@@ -832,6 +919,7 @@ int fg_chain_run(const fg_chain_t* ch, void* ws, size_t ws_bytes, fg_stream_t st
     }
     set = ch->smem_bytes;
   }
+  lk.unlock();
   uint8_t* wsb = static_cast<uint8_t*>(ws);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   e = cudaMemsetAsync(wsb + ch->off_done, 0, 4 * static_cast<size_t>(ch->count), s);
@@ -958,6 +1046,7 @@ int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* sc
 
 int fg_trace_enable(int on) {
   g_trace.store(on ? 1 : 0, std::memory_order_relaxed);
+  g_trace_seq.store(0, std::memory_order_relaxed);
   return FG_OK;
 }
 
@@ -999,8 +1088,8 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   fg_plan_t pl;
   const int sms = dev->sm_count < kNoAllocMaxGrid ? dev->sm_count : kNoAllocMaxGrid;
   // The built-in scratch holds 16-row partial tiles: plan (and run) in passes of at most 16 rows.
-  if ((st = fg_plan(FG_OP_F16_NK, M < 16 ? M : 16, N, K, sms, dev->smem_optin, &pl)) != FG_OK) return st;
-  if (pl.grid > kNoAllocMaxGrid || pl.m_tile > 16) return FG_ERR_WORKSPACE;
+  if ((st = fg_plan_tiled(FG_OP_F16_NK, M < 16 ? M : 16, N, K, sms, dev->smem_optin, &pl)) != FG_OK) return st;
+  if (pl.grid > kNoAllocMaxGrid || pl.m_tile > 16 || pl.math == 4) return FG_ERR_WORKSPACE;
   pl.pdl = 0;  // a memset precedes every launch, so there is no kernel to overlap with
 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -11,8 +11,9 @@
 #define FG_CHUNK_W_BYTES 16384     /* weight bytes per chunk                            */
 #define FG_RED_STRIDE 132          /* floats per row of the cross-warp reduction buffer */
 
-/* Workspace: [0,256) status word; then FG_MAX_GRID x 2 partial tiles of up to 64 x 128 fp32;
- * then one 32-bit arrival counter per output tile. */
+/* Workspace: [0,256) header (status word at 0, the GEMV kernel's counters at 64 and 128); then
+ * FG_MAX_GRID x 2 partial tiles of up to 64 x 128 fp32; then one 32-bit arrival counter per
+ * output tile. */
 #define FG_WS_HEADER_BYTES 256
 #define FG_MAX_M_TILE 64           /* tallest accumulator tile (tcgen05 fp16 kernel)    */
 #define FG_WS_PARTIAL_TILE_BYTES (FG_MAX_M_TILE * FG_TILE_N * 4)
@@ -36,11 +37,38 @@ static inline int fg_smem_bytes(int op, int m_tile, int chunks, int stages, int 
   return fg_fixed_smem_bytes(consumer_warps, m_tile) + stages * (chunks * fg_chunk_bytes(op, m_tile) + 16);
 }
 
+/* row-split GEMV kernel (math 4): x, ring of whole-row stages, cross-warp sums, stage table, barriers */
+#define FG_GEMV_MAX_M 2
+#define FG_GEMV_MAX_OUT 8                /* rows per stage x token rows */
+#define FG_GEMV_MAX_WARPS 12             /* consumer warps; each owns every warps-th stage */
+#define FG_GEMV_MIN_K 1024
+#define FG_GEMV_STAGE_TARGET_BYTES 16384 /* as many rows per stage as fit in this */
+#define FG_GEMV_MAX_STAGE_BYTES 65536    /* a stage holds at least one whole row */
+#define FG_GEMV_STATIC_PCT 100           /* share of the rows dealt out up front (whole stages); the rest on demand */
+#define FG_GEMV_L2_PREFETCH_BYTES 98304
+/* workspace header words of the GEMV kernel's row-block counter and exit counter */
+#define FG_WS_GEMV_NEXT_OFFSET 64
+#define FG_WS_GEMV_EXITED_OFFSET 128
+static inline int fg_gemv_fixed_smem_bytes(int M, int K) { return 127 + ((M * K * 2 + 127) & ~127) + 8; }
+/* per stage: the rows, the stage's row range, two barriers */
+static inline int fg_gemv_smem_bytes(int M, int K, int stage_bytes, int stages) {
+  return fg_gemv_fixed_smem_bytes(M, K) + stages * (stage_bytes + 8 + 16);
+}
+/* Consumer warps for a ring of `stages` slots: the largest divisor of stages up to FG_GEMV_MAX_WARPS
+ * (a slot must always meet the same warp). */
+static inline int fg_gemv_warps(int stages) {
+  int w = stages < FG_GEMV_MAX_WARPS ? stages : FG_GEMV_MAX_WARPS;
+  while (w > 1 && stages % w) --w;
+  return w;
+}
+
 /* tcgen05 variant for quantized weights: ring, 32 KB fp16 staging buffers, barriers */
 #ifdef __cplusplus
 struct fg_plan_t;
 extern "C" int fg_plan_mma_sync(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
                                 struct fg_plan_t* out); /* quantized ops: the mma.sync kernel's plan for any M */
+extern "C" int fg_plan_tiled(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
+                             struct fg_plan_t* out);    /* never the row-split GEMV kernel */
 #endif
 #define FG_UMMA_Q_STAGING_BYTES 98304 /* three 32 KB buffers */
 static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages);

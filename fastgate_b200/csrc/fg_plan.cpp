@@ -12,27 +12,84 @@
 #include "fg_layout.h"
 
 static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_bytes, fg_plan_t* out,
-                     bool force_mma_sync);
+                     bool force_mma_sync, bool allow_gemv);
 
 extern "C" int fg_plan(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
                        fg_plan_t* out) {
-  return plan_impl(op, M, N, K, sm_count, smem_optin_bytes, out, false);
+  return plan_impl(op, M, N, K, sm_count, smem_optin_bytes, out, false, true);
 }
 
 // Internal (fg_layout.h): the plan of the mma.sync kernel for a quantized op whatever M is.
 extern "C" int fg_plan_mma_sync(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
                                 fg_plan_t* out) {
-  return plan_impl(op, M, N, K, sm_count, smem_optin_bytes, out, true);
+  return plan_impl(op, M, N, K, sm_count, smem_optin_bytes, out, true, false);
+}
+
+// Internal (fg_layout.h): the plan of a tiled kernel even where fg_plan would pick the row-split
+// GEMV kernel (entry points that push tiles to other ranks or use the library's built-in scratch).
+extern "C" int fg_plan_tiled(int op, int M, int N, int K, int sm_count, int smem_optin_bytes,
+                             fg_plan_t* out) {
+  return plan_impl(op, M, N, K, sm_count, smem_optin_bytes, out, false, false);
+}
+
+// The row-split GEMV kernel takes NxK fp16 weights with up to four token rows when x fits in
+// 64 KB of shared memory, a weight row in one ring stage, and a row has a 16-byte piece for every
+// consumer thread.  (int8 weights stay with the tensor-core kernels: dequantising costs more issue
+// slots per byte than the CUDA cores have left at HBM speed.)
+static bool gemv_eligible(int op, int M, int K) {
+  return op == FG_OP_F16_NK && M <= FG_GEMV_MAX_M && K >= FG_GEMV_MIN_K && static_cast<long long>(M) * K * 2 <= 65536 &&
+         K * 2 <= FG_GEMV_MAX_STAGE_BYTES;
+}
+
+static int plan_gemv(int op, int M, int N, int K, int sm_count, int smem_optin_bytes, fg_plan_t* out) {
+  fg_plan_t p;
+  std::memset(&p, 0, sizeof(p));
+  p.op = op;
+  p.math = 4;
+  p.m_tile = M;
+  p.passes = 1;
+  p.tiles = N / 128;
+  p.pdl = 1;
+  const int row_bytes = K * 2;
+  int rows = FG_GEMV_MAX_OUT;
+  while (rows > 1 && (rows * row_bytes > FG_GEMV_STAGE_TARGET_BYTES || rows * M > FG_GEMV_MAX_OUT)) rows >>= 1;
+  p.rows_per_stage = rows;
+  p.k_per_stage = K;       // a stage holds whole rows
+  p.k_blocks = 1;
+  const int stage_bytes = rows * row_bytes;
+  const int fit = std::min((smem_optin_bytes - fg_gemv_fixed_smem_bytes(M, K)) / (stage_bytes + 24), FG_MAX_STAGES);
+  if (fit < 3) return FG_ERR_PLAN;  // rows too long for a useful ring: the tiled kernels take over
+  // ring depth: up to three slots are given up for a depth that more warps divide
+  int best_s = fit, best_w = fg_gemv_warps(fit);
+  for (int s2 = fit - 1; s2 >= 3 && s2 >= fit - 3; --s2)
+    if (fg_gemv_warps(s2) > best_w) {
+      best_w = fg_gemv_warps(s2);
+      best_s = s2;
+    }
+  p.stages = best_s;
+  p.consumer_warps = best_w;
+  const int blocks = (N + rows - 1) / rows;
+  p.grid = std::min(std::min(sm_count, FG_MAX_GRID), blocks);
+  // a fixed share first (its first ring-full needs no counter), the rest dealt out on demand
+  p.static_rows = static_cast<int>(static_cast<long long>(N) * FG_GEMV_STATIC_PCT / 100 / p.grid) / rows * rows;
+  p.smem_bytes = fg_gemv_smem_bytes(M, K, stage_bytes, p.stages);
+  *out = p;
+  return FG_OK;
 }
 
 static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_bytes, fg_plan_t* out,
-                     bool force_mma_sync) {
+                     bool force_mma_sync, bool allow_gemv) {
   if (out == nullptr) return FG_ERR_NULL;
   std::memset(out, 0, sizeof(*out));
   if (op < FG_OP_F16_KN || op > FG_OP_W4A16_NK) return FG_ERR_PLAN;
   if (M <= 0 || N <= 0 || K <= 0 || (N % 128) != 0 || (K % 128) != 0) return FG_ERR_SHAPE;
   if (sm_count <= 0) sm_count = 148;                 // B200
   if (smem_optin_bytes <= 0) smem_optin_bytes = 232448;  // 227 KB opt-in per CTA on sm_100
+
+  if (allow_gemv && gemv_eligible(op, M, K)) {
+    const int st = plan_gemv(op, M, N, K, sm_count, smem_optin_bytes, out);
+    if (st == FG_OK) return st;  // no room for a ring: fall through to the tiled kernels
+  }
 
   fg_plan_t p;
   std::memset(&p, 0, sizeof(p));
@@ -155,6 +212,24 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
   if (p == nullptr) return FG_ERR_NULL;
   if (smem_optin_bytes <= 0) smem_optin_bytes = 232448;
   if (p->op < FG_OP_F16_KN || p->op > FG_OP_W4A16_NK) return FG_ERR_PLAN;
+  if (p->math == 4) {
+    // row-split GEMV kernel
+    if (p->m_tile < 1 || p->m_tile > FG_GEMV_MAX_M || !gemv_eligible(p->op, p->m_tile, K)) return FG_ERR_PLAN;
+    if (p->rows_per_stage != 1 && p->rows_per_stage != 2 && p->rows_per_stage != 4 && p->rows_per_stage != 8) return FG_ERR_PLAN;
+    if (p->rows_per_stage * p->m_tile > FG_GEMV_MAX_OUT) return FG_ERR_PLAN;
+    const int row_bytes = K * (p->op == FG_OP_W8A16_NK ? 1 : 2);
+    const long long stage_bytes = static_cast<long long>(p->rows_per_stage) * row_bytes;
+    if (stage_bytes > FG_GEMV_MAX_STAGE_BYTES) return FG_ERR_PLAN;
+    if (p->stages < 2 || p->stages > FG_MAX_STAGES) return FG_ERR_PLAN;
+    if (p->consumer_warps < 1 || p->consumer_warps > FG_GEMV_MAX_WARPS || p->stages % p->consumer_warps) return FG_ERR_PLAN;
+    if (p->k_per_stage != K || p->k_blocks != 1 || p->tiles != N / 128 || p->passes != 1) return FG_ERR_PLAN;
+    if (p->grid < 1 || p->grid > FG_MAX_GRID) return FG_ERR_PLAN;
+    if (p->static_rows < 0 || p->static_rows % p->rows_per_stage ||
+        static_cast<long long>(p->static_rows) * p->grid > N) return FG_ERR_PLAN;
+    if (p->smem_bytes != fg_gemv_smem_bytes(p->m_tile, K, static_cast<int>(stage_bytes), p->stages)) return FG_ERR_PLAN;
+    if (p->smem_bytes > smem_optin_bytes) return FG_ERR_PLAN;
+    return FG_OK;
+  }
   const bool quantized = (p->op == FG_OP_W8A16_NK || p->op == FG_OP_W4A16_NK);
   if (p->m_tile != 8 && p->m_tile != 16 && p->m_tile != 32 && p->m_tile != 64) return FG_ERR_PLAN;
   if (p->m_tile > 16 && (p->math != 2 || p->op > FG_OP_F16_NK)) return FG_ERR_PLAN;  // tall tiles: fp16 tcgen05 kernel only
@@ -170,7 +245,7 @@ extern "C" int fg_plan_validate(const fg_plan_t* p, int N, int K, int smem_optin
     if (quantized && (chunks > 4 || p->m_tile != 16)) return FG_ERR_PLAN;
   } else {
     if (p->consumer_warps < 1 || p->consumer_warps > FG_MAX_CONSUMER_WARPS) return FG_ERR_PLAN;
-    // the dequantising kernels are built for <= 4 consumer warps (<= 3 with a 16-row tile)
+    // the dequantising kernels are built for <= 6 consumer warps (<= 3 with a 16-row tile)
     if (quantized && p->consumer_warps > (p->m_tile == 16 ? 3 : 6)) return FG_ERR_PLAN;
     // each stage must always meet the same consumer warp (see fg_plan)
     if (p->stages % p->consumer_warps) return FG_ERR_PLAN;

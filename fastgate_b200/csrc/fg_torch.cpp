@@ -30,8 +30,10 @@ std::mutex g_ws_mu;
 std::map<std::pair<int, int64_t>, Workspace> g_ws;
 
 // One workspace per (device, stream): calls on one stream are ordered, calls on different
-// streams may overlap and must not share partial tiles or arrival counters.
-Workspace& workspace_for(int device, cudaStream_t stream, int N) {
+// streams may overlap and must not share partial tiles or arrival counters.  Returned by value
+// (a tensor handle and its size): the handle keeps the memory alive for the caller even if
+// another thread replaces the map entry with a larger buffer meanwhile.
+Workspace workspace_for(int device, cudaStream_t stream, int N) {
   const size_t need = fg_workspace_bytes(N);
   std::lock_guard<std::mutex> lk(g_ws_mu);
   Workspace& w = g_ws[{device, reinterpret_cast<int64_t>(stream)}];
@@ -88,7 +90,7 @@ void linear(int op, const at::Tensor& x, const at::Tensor& W, at::Tensor& C, con
 
   const c10::cuda::CUDAGuard guard(x.device());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
-  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  const Workspace ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
   int st;
   {
     pybind11::gil_scoped_release nogil;
@@ -144,7 +146,7 @@ void op_wfirst_int4(at::Tensor W4, at::Tensor x, at::Tensor C, c10::optional<at:
   if ((N % 128) != 0 || (K % 128) != 0 || N <= 0 || K <= 0) raise(FG_ERR_SHAPE, true);
   const c10::cuda::CUDAGuard guard(x.device());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
-  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  const Workspace ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
   int st;
   {
     pybind11::gil_scoped_release nogil;
@@ -184,7 +186,7 @@ void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std
   }
   const c10::cuda::CUDAGuard guard(x.device());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
-  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  const Workspace ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
   int st;
   {
     pybind11::gil_scoped_release nogil;
@@ -198,7 +200,7 @@ void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std
 void push_wait(int64_t flag_ptr, int64_t world, int64_t target, int64_t device) {
   const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(device).stream();
-  Workspace& ws = workspace_for(static_cast<int>(device), stream, 128);
+  const Workspace ws = workspace_for(static_cast<int>(device), stream, 128);
   const int st = fg_push_wait(reinterpret_cast<const unsigned long long*>(flag_ptr), static_cast<int>(world),
                               static_cast<unsigned long long>(target), ws.buf.data_ptr(),
                               reinterpret_cast<fg_stream_t>(stream));
@@ -209,7 +211,7 @@ void push_wait(int64_t flag_ptr, int64_t world, int64_t target, int64_t device) 
 int64_t workspace_status(int64_t device) {
   const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(device).stream();
-  Workspace& ws = workspace_for(static_cast<int>(device), stream, 128);
+  const Workspace ws = workspace_for(static_cast<int>(device), stream, 128);
   int v = -1;
   const int st = fg_workspace_status(ws.buf.data_ptr(), &v, reinterpret_cast<fg_stream_t>(stream));
   if (st != FG_OK) raise(st, true);
@@ -261,7 +263,7 @@ void linear_fused(at::Tensor x, at::Tensor W, at::Tensor C, c10::optional<at::Te
   if ((N % 128) != 0 || (K % 128) != 0) raise(FG_ERR_SHAPE, op != FG_OP_F16_KN);
   const c10::cuda::CUDAGuard guard(x.device());
   cudaStream_t stream = at::cuda::getCurrentCUDAStream(x.get_device()).stream();
-  Workspace& ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
+  const Workspace ws = workspace_for(x.get_device(), stream, static_cast<int>(N));
   int st;
   {
     pybind11::gil_scoped_release nogil;

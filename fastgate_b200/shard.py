@@ -14,7 +14,13 @@ Every shard keeps the kernels' contract (N/g % 128 == 0).  The gather delivers
 128-column tile directly into the full ``C[M, N]`` of every rank through NVLink peer
 mappings (torch symmetric memory) and bumps each rank's arrival counter; a one-thread wait
 kernel then holds the stream until all ranks' tiles have landed.  No NCCL call, no
-``[g,M,N/g] -> [M,N]`` copy.  Plain peer stores only (no multimem, no TMA from peer memory).
+``[g,M,N/g] -> [M,N]`` copy.  Peer stores and atomics over NVLink mappings, or, from 8 ranks on
+(``FASTGATE_MULTIMEM=0|1`` overrides), one ``multimem.st`` / ``multimem.red`` per tile that the
+NVSwitch replicates to every rank; never a TMA access to peer memory.
+
+A layer's push buffers are rewritten by every rank as soon as that rank's next call on the layer
+runs: call ``forward_push`` on a layer again only after every rank has consumed the previous
+result (a barrier between rounds, or two layers / buffer sets used alternately).
 """
 from __future__ import annotations
 

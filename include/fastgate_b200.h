@@ -20,8 +20,9 @@
  *
  * All matrices are dense row-major.  fp16 is IEEE binary16 ("half").
  * Contract shared with the reference (hk/edgemm.cu:107-109): K % 128 == 0 and
- * N % 128 == 0, otherwise FG_ERR_SHAPE.  M may be any positive number; M > 16
- * is processed in 16-row passes (the weight is streamed once per pass).
+ * N % 128 == 0, otherwise FG_ERR_SHAPE.  M may be any positive number: one pass
+ * over the weight serves up to 64 token rows of fp16 weights and up to 16 rows of
+ * quantized weights; a larger M takes fg_plan_t.passes launches.
  * Results overwrite C (C = A.B); accumulation is fp32, one rounding to fp16.
  */
 #ifndef FASTGATE_B200_H_
@@ -67,20 +68,26 @@ enum {
  */
 typedef struct fg_plan_t {
   int op;            /* FG_OP_*                                               */
-  int m_tile;        /* 8 or 16: token rows held per accumulator tile          */
-  int k_per_stage;   /* K elements one pipeline stage covers                   */
+  int m_tile;        /* 8, 16, 32 or 64: token rows held per accumulator tile   */
+  int k_per_stage;   /* K elements one (full) pipeline stage covers            */
   int stages;        /* depth of the shared-memory ring                        */
-  int consumer_warps;/* warps doing the math (+1 warp issuing copies, +1 finishing split tiles) */
+  int consumer_warps;/* warps doing the math (+1 warp issuing copies, + warps finishing split tiles) */
   int grid;          /* persistent CTAs                                        */
   int tiles;         /* N / 128                                                */
   int k_blocks;      /* ceil(K / k_per_stage): stages per output tile          */
   int smem_bytes;    /* dynamic shared memory per CTA                          */
-  int passes;        /* ceil(M / 16) launches                                  */
-  int math;          /* 0 = mma.sync tiles, accumulators in registers; 2 = tcgen05.mma, accumulator
-                        in tensor memory (fp16 weights, m_tile 16); 1 reserved                */
+  int passes;        /* launches per call: ceil(M / 64) for fp16 weights on the tcgen05 kernel,
+                        ceil(M / 16) otherwise                                  */
+  int math;          /* 0 = mma.sync tiles, accumulators in registers; 2 = tcgen05.mma, accumulator in
+                        tensor memory; 4 = row-split GEMV kernel (mixed-precision FMA, whole weight
+                        rows per CTA, no reduction between CTAs; then m_tile = M <= 2, k_per_stage = K,
+                        k_blocks = 1); 1 and 3 reserved                                   */
   int pdl;           /* 1 = programmatic dependent launch: the kernel may start, and prefetch
                         weight tiles, while the previous kernel of the stream drains; it reads
                         activations and writes nothing before that kernel has completed       */
+  int rows_per_stage;/* math 4: weight rows per ring stage (1, 2, 4 or 8); else 0         */
+  int static_rows;   /* math 4: rows every CTA streams before it takes blocks of rows_per_stage
+                        rows from the shared counter (a multiple of rows_per_stage); else 0 */
 } fg_plan_t;
 
 /* Pure host function (callable without a GPU): fills *out for a problem on a device
@@ -94,9 +101,12 @@ int fg_plan_validate(const fg_plan_t* plan, int N, int K, int smem_optin_bytes);
  * Split-K partial tiles and per-tile arrival counters live in caller-owned device
  * memory, 256-byte aligned.  fg_workspace_bytes() is an upper bound for any M and
  * K at the given N.  The workspace must be cleared once with fg_workspace_init()
- * before first use; after that every call leaves the counters at zero again, so no
- * memset is launched per call.  One workspace serves one stream at a time: calls
- * that may overlap on the GPU need separate workspaces. */
+ * before first use; after that every call leaves the counters at zero again,
+ * so no memset is launched per call.  The exception is a call that reported
+ * FG_ERR_TIMEOUT or FG_ERR_PLAN in the status word: a wait that gave up leaves its
+ * counters as they were, so clear the workspace again with
+ * fg_workspace_init() before the next call.  One workspace serves one stream at a
+ * time: calls that may overlap on the GPU need separate workspaces. */
 size_t fg_workspace_bytes(int N);
 int fg_workspace_init(void* ws, size_t ws_bytes, fg_stream_t stream);
 /* Synchronises `stream`, copies the device status word to *status_out (FG_OK,
@@ -157,8 +167,10 @@ int fg_quantize_rows_w4(const void* W, uint8_t* W4, void* scales, int groups, in
 int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, int K,
                            fg_stream_t stream);
 
-/* Same three operations with an explicit plan (from fg_plan, possibly edited):
- * used by the tuner and the tests that walk every plan the heuristic can emit. */
+/* The fp16 and int8 operations with an explicit plan (from fg_plan, possibly edited):
+ * used by the tuner and the tests that walk every plan the heuristic can emit.  int4 plans
+ * are refused (FG_ERR_PLAN): that op needs its group count and zero point, which
+ * fg_gemm_w4a16_nk takes. */
 int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const void* scales,
                     void* C, int M, int N, int K, void* ws, size_t ws_bytes, fg_stream_t stream);
 
@@ -169,7 +181,9 @@ int fg_gemm_planned(const fg_plan_t* plan, const void* x, const void* W, const v
  * into the full output C[M, n_total] of EVERY rank (plain stores through NVLink peer
  * mappings: symmetric memory, CUDA IPC or cudaDeviceEnablePeerAccess) and then adds 1 to
  * counter [rank] of every rank's flag array (eight 64-bit counters, one per source rank).
- * A call by rank r adds N_local/128 * ceil(M/16) to counter [r] on every rank;
+ * A call by rank r adds N_local/128 * passes to counter [r] on every rank, where passes is
+ * fg_plan(FG_OP_F16_NK, M, N_local, K, ...).passes = ceil(M/64) (every pass over the weight
+ * delivers each of the rank's tiles once);
  * fg_push_wait enqueues a one-thread kernel that waits, for at most 2 s, until counters
  * [0, world) of the local flag array have all reached `target` (the caller keeps the running
  * total per rank), after which the full output is complete on this rank.  No rank's compute
@@ -195,6 +209,10 @@ typedef struct fg_peers_t {
   unsigned long long* mc_flag;
 } fg_peers_t;
 
+/* A layer's output buffers are written by every rank as soon as that rank's kernel runs: push
+ * into the same buffers again only after every rank has finished reading the previous result
+ * (the counters order a rank's reads after the pushes, not the next push after the reads); use
+ * two alternating sets of buffers, or a barrier between rounds. */
 int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, int K,
                         const fg_peers_t* peers, void* ws, size_t ws_bytes, fg_stream_t stream);
 int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long long target, void* ws,

@@ -11,7 +11,9 @@ The result serves two purposes, both as a checker / comparator, never as the pro
   * GPU tests compare the new kernels with the reference's kernels on identical inputs;
   * bench.py can time the reference's kernels on the same B200.
 
-Usage: python oracle/build_ref.py [/path/to/reference]     (default /root/reference)
+Usage: python oracle/build_ref.py [/path/to/reference]
+The checkout is looked for at the argument, else at $FASTGATE_REFERENCE; without either (or
+when the path does not exist) nothing is built and an earlier build is reused.
 """
 from __future__ import annotations
 
@@ -26,10 +28,17 @@ OUT = os.path.join(HERE, "_ref")
 SOURCES = ("hk/edgemm.cu", "hk/edgemm_tr.cu", "hk/flatgemm.cu", "hk/fastgemv.cu", "czn/fastgemm.cu")
 
 
-def build(reference: str = "/root/reference", force: bool = False) -> str | None:
+def reference_root() -> str | None:
+    """The reference checkout named by $FASTGATE_REFERENCE, if it is there."""
+    root = os.environ.get("FASTGATE_REFERENCE", "")
+    return root if root and os.path.isdir(os.path.join(root, "backend", "cuda")) else None
+
+
+def build(reference: str | None = None, force: bool = False) -> str | None:
+    reference = reference or reference_root() or ""
     cuda_dir = os.path.join(reference, "backend", "cuda")
     target = os.path.join(OUT, "fastgate_ref.so")
-    if not os.path.isdir(cuda_dir):
+    if not reference or not os.path.isdir(cuda_dir):
         return target if os.path.exists(target) else None
     if os.path.exists(target) and not force:
         return target
@@ -74,4 +83,5 @@ def build(reference: str = "/root/reference", force: bool = False) -> str | None
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv))
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(build(args[0] if args else None, force="--force" in sys.argv))

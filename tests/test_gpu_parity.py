@@ -202,7 +202,8 @@ def test_linearity_and_row_independence(dev, ws):
     eight = torch.zeros(8, 8192, dtype=torch.float16, device=dev)
     assert gu.call(wl.OP_NK, xd[2:3].contiguous(), Wd, None, one, 1, 8192, 8192, ws) == capi.FG_OK
     assert gu.call(wl.OP_NK, xd[0:8].contiguous(), Wd, None, eight, 8, 8192, 8192, ws) == capi.FG_OK
-    assert torch.equal(one.view(torch.int16), eight[2:3].view(torch.int16))
+    # one row runs in the row-split GEMV kernel, eight in a tiled one: other summation order
+    assert _one_rounding_step_apart(one, eight[2:3])
     # a zero row gives exactly zero, scaling by two is exact in fp16
     z = torch.zeros(2, 8192, dtype=torch.float16, device=dev)
     out = torch.ones(2, 8192, dtype=torch.float16, device=dev)

@@ -57,7 +57,8 @@ def simulate(tiles, k_blocks, grid):
     return contrib
 
 
-SHAPES = [(1, 16, 8192, 8192), (1, 1, 11008, 4096), (1, 1, 4096, 11008), (0, 8, 4096, 4096),
+SHAPES = [(1, 1, 8192, 8192), (1, 2, 8192, 8192), (1, 2, 3072, 12288), (1, 1, 128, 1024), (1, 1, 256, 32768), (1, 2, 128, 128),
+          (1, 16, 8192, 8192), (1, 1, 11008, 4096), (1, 1, 4096, 11008), (0, 8, 4096, 4096),
           (2, 1, 28672, 8192), (2, 8, 28672, 8192), (1, 16, 9216, 3072), (1, 16, 3072, 3072),
           (1, 16, 12288, 3072), (1, 16, 3072, 12288), (1, 4, 128, 128), (0, 3, 256, 384),
           (1, 16, 1152, 3072), (1, 16, 384, 3072), (1, 16, 1536, 3072), (1, 33, 4096, 4096),
@@ -66,10 +67,37 @@ SHAPES = [(1, 16, 8192, 8192), (1, 1, 11008, 4096), (1, 1, 4096, 11008), (0, 8, 
           (2, 40, 4096, 4096)]
 
 
+def check_gemv_plan(p, M, N, K):
+    """Row-split GEMV kernel (math 4): every weight row is streamed exactly once, by one CTA."""
+    assert p.op == 1 and 1 <= M <= 2 and p.m_tile == M and p.passes == 1
+    assert p.rows_per_stage in (1, 2, 4, 8) and p.rows_per_stage * M <= 8
+    assert p.rows_per_stage * K * 2 <= 65536 and p.k_per_stage == K and p.k_blocks == 1
+    assert 3 <= p.stages <= 24 and 1 <= p.consumer_warps <= 12 and p.stages % p.consumer_warps == 0
+    assert 1 <= p.grid <= 148 and p.smem_bytes <= 232448
+    assert p.static_rows % p.rows_per_stage == 0 and p.static_rows * p.grid <= N
+    # static shares, then blocks of rows_per_stage rows from the counter, cover [0, N) once
+    covered = [0] * N
+    for c in range(p.grid):
+        for r in range(c * p.static_rows, (c + 1) * p.static_rows):
+            covered[r] += 1
+    dyn0, j = p.grid * p.static_rows, 0
+    while dyn0 + j * p.rows_per_stage < N:
+        for r in range(dyn0 + j * p.rows_per_stage, min(N, dyn0 + (j + 1) * p.rows_per_stage)):
+            covered[r] += 1
+        j += 1
+    assert all(v == 1 for v in covered)
+    assert j <= 2 * p.grid, "only the remainder is dealt out on demand"
+
+
 @pytest.mark.parametrize("op,M,N,K", SHAPES)
 def test_plan_invariants(op, M, N, K):
     p = capi.plan(op, M, N, K, **B200)
     assert p.op == op and p.tiles == N // 128
+    if p.math == 4:
+        check_gemv_plan(p, M, N, K)
+        assert capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK
+        return
+    assert not (op == 1 and M <= 2 and 1024 <= K <= 16384), "NxK fp16 weights with one or two rows: the GEMV kernel"
     assert p.m_tile in (8, 16, 32, 64) and (p.m_tile >= 16 or M <= 8)
     assert p.m_tile >= min(M, 16)
     assert p.m_tile <= 16 or (op in (0, 1) and p.math == 2), "tall tiles: fp16 tcgen05 kernel only"
@@ -151,6 +179,30 @@ def test_validate_catches_edited_plans():
     assert edited2(m_tile=8) == capi.FG_ERR_PLAN
     assert edited2(op=2) == capi.FG_ERR_PLAN
     assert edited2(math=0) == capi.FG_ERR_PLAN          # another kernel, another shared-memory layout
+
+
+def test_validate_catches_edited_gemv_plans():
+    L = capi.lib
+    good = capi.plan(1, 1, 8192, 8192, **B200)
+    assert good.math == 4
+
+    def edited(**kw):
+        q = capi.Plan()
+        ctypes.memmove(ctypes.byref(q), ctypes.byref(good), ctypes.sizeof(q))
+        for k, v in kw.items():
+            setattr(q, k, v)
+        return L.fg_plan_validate(ctypes.byref(q), 8192, 8192, 232448)
+
+    assert edited() == capi.FG_OK
+    assert edited(static_rows=0) == capi.FG_OK                      # everything on demand
+    assert edited(static_rows=56) == capi.FG_ERR_PLAN               # 148 x 56 rows > N
+    assert edited(rows_per_stage=3) == capi.FG_ERR_PLAN
+    assert edited(rows_per_stage=8) == capi.FG_ERR_PLAN             # 128 KB per stage
+    assert edited(consumer_warps=5) == capi.FG_ERR_PLAN             # must divide the ring depth
+    assert edited(stages=good.stages + 1) == capi.FG_ERR_PLAN       # shared memory no longer matches
+    assert edited(m_tile=3) == capi.FG_ERR_PLAN
+    assert edited(op=0) == capi.FG_ERR_PLAN                         # KxN weights have no contiguous rows
+    assert edited(math=2) == capi.FG_ERR_PLAN
 
 
 def test_default_device_is_b200():
