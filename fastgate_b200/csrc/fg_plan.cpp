@@ -6,6 +6,7 @@
 // Here there is no split-K factor to pick: the (tile, k-block) list is dealt evenly to
 // one persistent CTA per SM, so the plan only fixes the pipeline shape.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/fastgate_b200.h"
@@ -36,8 +37,18 @@ extern "C" int fg_plan_tiled(int op, int M, int N, int K, int sm_count, int smem
 // 64 KB of shared memory, a weight row in one ring stage, and a row has a 16-byte piece for every
 // consumer thread.  (int8 weights stay with the tensor-core kernels: dequantising costs more issue
 // slots per byte than the CUDA cores have left at HBM speed.)
+static int gemv_max_m() {
+  // FASTGATE_GEMV_MAX_M=0|1|2 narrows the kernel's range (0: never), for A/B measurements
+  static const int v = [] {
+    const char* e = std::getenv("FASTGATE_GEMV_MAX_M");
+    const int n = (e != nullptr && e[0] >= '0' && e[0] <= '9') ? e[0] - '0' : FG_GEMV_MAX_M;
+    return n < FG_GEMV_MAX_M ? n : FG_GEMV_MAX_M;
+  }();
+  return v;
+}
+
 static bool gemv_eligible(int op, int M, int K) {
-  return op == FG_OP_F16_NK && M <= FG_GEMV_MAX_M && K >= FG_GEMV_MIN_K && static_cast<long long>(M) * K * 2 <= 65536 &&
+  return op == FG_OP_F16_NK && M <= gemv_max_m() && K >= FG_GEMV_MIN_K && static_cast<long long>(M) * K * 2 <= 65536 &&
          K * 2 <= FG_GEMV_MAX_STAGE_BYTES;
 }
 

@@ -143,27 +143,36 @@ class ShardedLinear:
         return self.assemble(self.gather(self.forward_local(x)))
 
     # ---- fused all-gather -----------------------------------------------------------------
-    def push_buffers(self, m_max: int, device) -> "PushBuffers":
-        """Collective: allocate (once per m_max) the symmetric output of this layer."""
-        key = ("push", m_max)
+    def push_buffers(self, m_max: int, device, slot=0) -> "PushBuffers":
+        """Collective: allocate (once per m_max and slot) a symmetric output of this layer."""
+        key = ("push", m_max, slot)
         if key not in self._bufs:
             self._bufs[key] = PushBuffers(m_max, self.n_total, device, self.group)
         return self._bufs[key]
 
-    def forward_push(self, x: torch.Tensor, wait: bool = True, after: Optional["PushBuffers"] = None) -> torch.Tensor:
+    def forward_push(self, x: torch.Tensor, wait: bool = True, after: Optional["PushBuffers"] = None, slot=0,
+                     into: Optional["PushBuffers"] = None) -> torch.Tensor:
         """Full C[M, N] on every rank with the all-gather fused into the kernel's epilogue.
 
         wait=False: the caller makes sure the result is complete before touching it, either
         with `push_wait` or by handing this layer's buffers as `after=` to the next layer.
         after=: x is the pushed output of that earlier layer; the kernel streams its first
         weight tiles at once and reads x only when every rank's tiles of that layer have landed.
+        slot=: which of the layer's output buffer sets to push into (any hashable; every rank must
+        use the same sequence).  A set may be pushed into again only when every rank has consumed
+        what it held: callers that keep several results alive, or have several steps in flight,
+        rotate over slots.
+        into=: push into these buffers (made by the caller with PushBuffers(m_max, n_total, device))
+        instead of one of the layer's own sets; the same rule applies.
         """
         from . import ops
 
         if self.w.dtype != torch.float16:
             raise NotImplementedError("the fused all-gather is implemented for fp16 NxK weights")
         M = x.shape[0]
-        pb = self.push_buffers(max(M, 16), x.device)
+        pb = into if into is not None else self.push_buffers(max(M, 16), x.device, slot)
+        if pb.n_total != self.n_total or pb.out.shape[0] < M:
+            raise ValueError("fastgate_b200: push buffers do not fit this layer's output")
         wait_ptr, wait_target = (after.flag_ptrs[after.rank], after.target) if after is not None else (0, 0)
         ops.linear_nk_push(x, self.w, pb.c_ptrs, pb.flag_ptrs, pb.rank, self.n_total, wait_ptr, wait_target,
                            pb.mc_out, pb.mc_flag)
@@ -173,9 +182,9 @@ class ShardedLinear:
             self.push_wait(pb)
         return pb.out[:M]
 
-    def last_push(self, M: int) -> "PushBuffers":
-        """The buffers the last forward_push with M rows wrote (to hand on as `after=`)."""
-        return self._bufs[("push", max(M, 16))]
+    def last_push(self, M: int, slot=0) -> "PushBuffers":
+        """The buffers forward_push with M rows and this slot writes (to hand on as `after=`)."""
+        return self._bufs[("push", max(M, 16), slot)]
 
     def push_wait(self, pb: "PushBuffers") -> None:
         from . import ops
