@@ -26,6 +26,10 @@ except (ImportError, AttributeError) as _e:  # missing or stale build
     def __getattr__(name):
         # Submodules that need no native code (build, workloads) stay importable so that the
         # extension can be (re)built; every operator fails loudly.
+        if name in ("build", "workloads"):
+            import importlib
+
+            return importlib.import_module(f"{__name__}.{name}")
         raise ImportError(
             f"fastgate_b200.{name}: the native extension fastgate_b200/_C.so is missing, unloadable or older than "
             "the Python package; run `python -m fastgate_b200.build` (there is no CPU fallback)") from _import_error

@@ -23,6 +23,7 @@ EXPORTS = (
     "fg_gemm_f16_nk_push", "fg_push_wait", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
     "fg_group_tiles", "fg_group_destroy", "fg_chain_table_bytes", "fg_chain_create", "fg_chain_workspace_bytes",
     "fg_chain_run", "fg_chain_grid", "fg_chain_trace_offset", "fg_chain_destroy", "fg_quantize_rows_w8", "fg_gemm_fused", "fg_linear_host",
+    "fg_prepack_kn_to_nk", "fg_prepack_gate_up",
     "fg_trace_enable", "fg_trace_read", "fg_status_str", "fg_last_cuda_error", "fg_launch_count", "fg_version",
 )
 
@@ -50,10 +51,11 @@ class Peers(ctypes.Structure):
 class Epilogue(ctypes.Structure):
     """Mirror of fg_epilogue_t."""
 
-    _fields_ = [("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("act", ctypes.c_int)]
+    _fields_ = [("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("act", ctypes.c_int),
+                ("split1", ctypes.c_int), ("split2", ctypes.c_int), ("C2", ctypes.c_void_p), ("C3", ctypes.c_void_p)]
 
 
-ACT = {"none": 0, "gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3}
+ACT = {"none": 0, "gelu": 1, "gelu_erf": 1, "gelu_tanh": 2, "silu": 3, "silu_gate": 4}
 
 
 class Problem(ctypes.Structure):
@@ -118,6 +120,8 @@ def _load() -> ctypes.CDLL:
     L.fg_quantize_rows_w8.argtypes = [vp, vp, vp, i, i, vp]
     L.fg_quantize_rows_w4.argtypes = [vp, vp, vp, i, i, i, vp]
     L.fg_gemm_fused.argtypes = [i, vp, vp, vp, vp, i, i, i, ctypes.POINTER(Epilogue), vp, sz, vp]
+    L.fg_prepack_kn_to_nk.argtypes = [vp, vp, i, i, vp]
+    L.fg_prepack_gate_up.argtypes = [vp, vp, vp, i, i, vp]
     L.fg_linear_host.argtypes = [i, vp, vp, vp, vp, vp, vp, i, i, i, vp, sz, vp]
     L.fg_trace_enable.argtypes = [i]
     L.fg_trace_read.argtypes = [vp, ctypes.POINTER(ctypes.c_ulonglong), i, vp]

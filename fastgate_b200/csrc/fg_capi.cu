@@ -28,7 +28,7 @@ static_assert(FG_MAX_CONSUMER_WARPS == fg::kMaxConsumerWarps, "layout mismatch")
 static_assert(int(FG_ERR_TIMEOUT) == int(fg::kStatusTimeout), "status mismatch");
 static_assert(int(FG_ERR_PLAN) == int(fg::kStatusBadLaunch), "status mismatch");
 static_assert(int(FG_ACT_GELU_ERF) == int(fg::kActGeluErf) && int(FG_ACT_GELU_TANH) == int(fg::kActGeluTanh) &&
-                  int(FG_ACT_SILU) == int(fg::kActSilu),
+                  int(FG_ACT_SILU) == int(fg::kActSilu) && int(FG_ACT_SILU_GATE) == int(fg::kActSiluGate),
               "activation code mismatch");
 static_assert(int(FG_OP_F16_KN) == int(fg::kOpF16KN) && int(FG_OP_F16_NK) == int(fg::kOpF16NK) &&
                   int(FG_OP_W8A16_NK) == int(fg::kOpW8A16NK) && int(FG_OP_W4A16_NK) == int(fg::kOpW4A16NK),
@@ -256,6 +256,10 @@ int run_gemv(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
   p.bias = ep ? static_cast<const __half*>(ep->bias) : nullptr;
   p.residual = ep ? static_cast<const __half*>(ep->residual) : nullptr;
   p.act = ep ? ep->act : 0;
+  p.split1 = ep ? ep->split1 : 0;
+  p.split2 = ep ? ep->split2 : 0;
+  p.C2 = ep ? static_cast<__half*>(ep->C2) : nullptr;
+  p.C3 = ep ? static_cast<__half*>(ep->C3) : nullptr;
   p.M = M;
   p.N = N;
   p.K = K;
@@ -355,6 +359,11 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.bias = ep ? static_cast<const __half*>(ep->bias) : nullptr;
   p.residual = nullptr;
   p.act = ep ? ep->act : 0;
+  p.split1 = ep ? ep->split1 : 0;
+  p.split2 = ep ? ep->split2 : 0;
+  p.C2 = ep ? static_cast<__half*>(ep->C2) : nullptr;
+  p.C3 = ep ? static_cast<__half*>(ep->C3) : nullptr;
+  if (peers != nullptr && (p.split1 != 0 || p.act == FG_ACT_SILU_GATE)) return FG_ERR_PLAN;  // a pushed output is one plain tensor
   p.world = 0;
   p.rank = 0;
   p.col0 = 0;
@@ -390,10 +399,15 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
     CUtensorMap tmX;
     st = encode_2d(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xp, K, mp, 64, pl.m_tile);
     if (st != FG_OK) return st;
-    p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * N;
+    const int width = (p.act == FG_ACT_SILU_GATE) ? N / 2 : N;  // row length of the output (and of the residual)
+    p.C = static_cast<__half*>(C) + static_cast<size_t>(m0) * (p.split1 ? p.split1 : width);
+    if (p.split1) {
+      p.C2 = static_cast<__half*>(ep->C2) + static_cast<size_t>(m0) * (p.split2 - p.split1);
+      p.C3 = static_cast<__half*>(ep->C3) + static_cast<size_t>(m0) * (N - p.split2);
+    }
     p.M = mp;
     if (ep != nullptr && ep->residual != nullptr)
-      p.residual = static_cast<const __half*>(ep->residual) + static_cast<size_t>(m0) * N;
+      p.residual = static_cast<const __half*>(ep->residual) + static_cast<size_t>(m0) * width;
     if (peers != nullptr) {
       for (int q = 0; q < peers->world; ++q)
         p.peer_C[q] = static_cast<__half*>(peers->C[q]) + static_cast<size_t>(m0) * peers->n_total;
@@ -1004,18 +1018,70 @@ int fg_gemm_fused(int op, const void* x, const void* W, const void* scales, void
   if (op < FG_OP_F16_KN || op > FG_OP_W8A16_NK) return FG_ERR_PLAN;
   int st = check_common(x, W, C, M, N, K, ws, ws_bytes);
   if (st != FG_OK) return st;
+  bool gate = false;
   if (ep != nullptr) {
-    if (ep->act < FG_ACT_NONE || ep->act > FG_ACT_SILU) return FG_ERR_PLAN;
+    if (ep->act < FG_ACT_NONE || ep->act > FG_ACT_SILU_GATE) return FG_ERR_PLAN;
     if ((reinterpret_cast<uintptr_t>(ep->bias) & 1u) != 0 || (reinterpret_cast<uintptr_t>(ep->residual) & 1u) != 0)
       return FG_ERR_ALIGN;
+    gate = (ep->act == FG_ACT_SILU_GATE);
+    if (gate && (op != FG_OP_F16_NK || ep->split1 != 0)) return FG_ERR_PLAN;  // interleaved NxK fp16 weights, one output
+    if (ep->split1 != 0 || ep->split2 != 0) {
+      if (ep->split1 <= 0 || ep->split2 < ep->split1 || ep->split2 > N || (ep->split1 % 8) != 0 || (ep->split2 % 8) != 0)
+        return FG_ERR_SHAPE;
+      if ((ep->split2 > ep->split1 && ep->C2 == nullptr) || (N > ep->split2 && ep->C3 == nullptr)) return FG_ERR_NULL;
+      if (!aligned16(ep->C2) || !aligned16(ep->C3)) return FG_ERR_ALIGN;
+    }
   }
   if (scales != nullptr && (reinterpret_cast<uintptr_t>(scales) & 3u) != 0) return FG_ERR_ALIGN;
   DeviceInfo* dev = nullptr;
   if ((st = device_info(&dev)) != FG_OK) return st;
   fg_plan_t pl;
-  if ((st = fg_plan(op, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+  if (gate) {
+    // the tcgen05 kernel, whose epilogue warps swap gate and up sums through 8 KB more of shared memory
+    if ((st = fg_plan_tiled(op, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) return st;
+    if (pl.math != 2) return FG_ERR_PLAN;
+    pl.smem_bytes += static_cast<int>(fg::kGateXchBytes);
+    if (pl.smem_bytes > dev->smem_optin) return FG_ERR_PLAN;
+  } else if ((st = fg_plan(op, M, N, K, dev->sm_count, dev->smem_optin, &pl)) != FG_OK) {
+    return st;
+  }
   return run_planned(pl, dev, x, W, op == FG_OP_W8A16_NK ? scales : nullptr, C, M, N, K, ws,
                      reinterpret_cast<cudaStream_t>(stream), nullptr, ep);
+}
+
+// ---- one-time weight repacking ---------------------------------------------------------------
+int fg_prepack_kn_to_nk(const void* B, void* W, int N, int K, fg_stream_t stream) {
+  if (B == nullptr || W == nullptr) return FG_ERR_NULL;
+  if (N <= 0 || K <= 0 || (N % 64) != 0 || (K % 64) != 0) return FG_ERR_SHAPE;
+  if (!aligned16(B) || !aligned16(W)) return FG_ERR_ALIGN;
+  const dim3 grid(N / 64, K / 64);
+  fg::fg_transpose_kn_to_nk_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(B), static_cast<__half*>(W), N, K);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
+int fg_prepack_gate_up(const void* Wg, const void* Wu, void* Wgu, int N, int K, fg_stream_t stream) {
+  if (Wg == nullptr || Wu == nullptr || Wgu == nullptr) return FG_ERR_NULL;
+  if (N <= 0 || K <= 0 || (N % 64) != 0 || (K % 128) != 0) return FG_ERR_SHAPE;
+  if (!aligned16(Wg) || !aligned16(Wu) || !aligned16(Wgu)) return FG_ERR_ALIGN;
+  // blocks of 64 rows are contiguous in all three matrices: 2 * N / 64 plain copies as one kernel
+  const long long chunks16 = static_cast<long long>(64) * K * 2 / 16;  // 16-byte pieces per block of rows
+  const dim3 grid(static_cast<unsigned>((chunks16 + 1023) / 1024), 2 * (N / 64));
+  fg::fg_interleave_gate_up_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(Wg), static_cast<const uint4*>(Wu), static_cast<uint4*>(Wgu), static_cast<int>(chunks16));
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
 }
 
 int fg_linear_host(int op, const void* x_host, const void* W_dev, const void* scales_dev, void* C_host,
@@ -1116,6 +1182,8 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   p.bias = nullptr;
   p.residual = nullptr;
   p.act = 0;
+  p.split1 = p.split2 = 0;
+  p.C2 = p.C3 = nullptr;
   p.mc_C = nullptr;
   p.mc_flag = nullptr;
   p.scale_groups = 1;

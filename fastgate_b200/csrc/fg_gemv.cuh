@@ -47,6 +47,9 @@ struct GemvParams {
   const __half* bias;        // [N] or nullptr
   const __half* residual;    // [M, N] or nullptr
   int act;
+  int split1, split2;        // output columns split over C, C2, C3 (see KParams); split1 == 0: all in C
+  __half* C2;
+  __half* C3;
   int M, N, K;
   int rows_per_stage;        // 1, 2, 4 or 8, times M at most kGemvMaxOut
   int stage_bytes;           // ring slot size = rows_per_stage * bytes per row
@@ -325,7 +328,12 @@ __global__ void __launch_bounds__((kGemvMaxWarps + 1) * 32, 1) fg_gemv_kernel(co
           default: break;
         }
         if (p.residual != nullptr) v += __half2float(p.residual[static_cast<size_t>(m) * p.N + n]);
-        p.C[static_cast<size_t>(m) * p.N + n] = __float2half_rn(v);
+        __half* dst;
+        if (p.split1 == 0) dst = p.C + static_cast<size_t>(m) * p.N + n;
+        else if (n < p.split1) dst = p.C + static_cast<size_t>(m) * p.split1 + n;
+        else if (n < p.split2) dst = p.C2 + static_cast<size_t>(m) * (p.split2 - p.split1) + (n - p.split1);
+        else dst = p.C3 + static_cast<size_t>(m) * (p.N - p.split2) + (n - p.split2);
+        *dst = __float2half_rn(v);
       }
       if (trace && lane == 0) {
         t_wait += tc1 - tc0;

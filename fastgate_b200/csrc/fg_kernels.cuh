@@ -47,7 +47,7 @@ constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s per wait, th
 
 enum { kOpF16KN = 0, kOpF16NK = 1, kOpW8A16NK = 2, kOpW4A16NK = 3 };
 enum { kStatusOk = 0, kStatusTimeout = 6, kStatusBadLaunch = 7 };
-enum { kActNone = 0, kActGeluErf = 1, kActGeluTanh = 2, kActSilu = 3 };
+enum { kActNone = 0, kActGeluErf = 1, kActGeluTanh = 2, kActSilu = 3, kActSiluGate = 4 };
 
 template <int OP>
 struct OpTraits;
@@ -94,7 +94,16 @@ struct KParams {
   //   out = act(acc * scale + bias[n]) + residual[m, n]
   const __half* bias;        // [N] or nullptr
   const __half* residual;    // [M, N] (this call's rows and columns) or nullptr
-  int act;                   // kActNone, kActGeluErf, kActGeluTanh, kActSilu
+  int act;                   // kActNone, kActGeluErf, kActGeluTanh, kActSilu, kActSiluGate
+  // kActSiluGate (tcgen05 fp16 kernel, NxK weights): the weight holds, per 128 rows, 64 rows of the gate
+  // projection followed by the matching 64 rows of the up projection; the output has N / 2 columns,
+  //   out[m, 64 t + j] = silu(acc[128 t + j] + bias) * (acc[128 t + 64 + j] + bias) + residual[m, 64 t + j]
+  // Optional split of the output columns over up to three dense tensors (a fused QKV projection):
+  // columns [0, split1) go to C, [split1, split2) to C2, [split2, N) to C3, each with its own row
+  // length; split1 == 0: everything goes to C.  split1 and split2 are multiples of 8.
+  int split1, split2;
+  __half* C2;
+  __half* C3;
   // Fused all-gather ("push") of an N-sharded layer: when world > 0 the output tile is stored
   // into the full [M, ldc] output of every rank at column col0 + n, and each finished tile
   // bumps every rank's arrival counter.  Plain stores and atomics over NVLink peer mappings.
@@ -371,6 +380,26 @@ __device__ __forceinline__ void with_act(int act, F&& f) {
   }
 }
 
+// Where output element (m, n) lives: C[M, N], or one of the three tensors of a split output.
+__device__ __forceinline__ __half* out_ptr(const KParams& p, int m, int n) {
+  if (p.split1 == 0) return p.C + static_cast<size_t>(m) * p.N + n;
+  if (n < p.split1) return p.C + static_cast<size_t>(m) * p.split1 + n;
+  if (n < p.split2) return p.C2 + static_cast<size_t>(m) * (p.split2 - p.split1) + (n - p.split1);
+  return p.C3 + static_cast<size_t>(m) * (p.N - p.split2) + (n - p.split2);
+}
+
+// One output of the SiLU-gated pair: g and u are the fp32 sums of gate row and up row `j` of tile `tile`.
+__device__ __forceinline__ void store_gate(const KParams& p, int m, int tile, int j, float g, float u) {
+  if (p.bias != nullptr) {
+    g += __half2float(p.bias[tile * kTileN + j]);
+    u += __half2float(p.bias[tile * kTileN + 64 + j]);
+  }
+  const int n_out = tile * 64 + j, width = p.N >> 1;
+  float v = act_fn<kActSilu>(g) * u;
+  if (p.residual != nullptr) v += __half2float(p.residual[static_cast<size_t>(m) * width + n_out]);
+  p.C[static_cast<size_t>(m) * width + n_out] = __float2half_rn(v);
+}
+
 // bias, activation and residual of one output element (fp32).
 template <int ACT>
 __device__ __forceinline__ float epilogue1(const KParams& p, int m, int n, float v) {
@@ -394,7 +423,7 @@ __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float
   }
   const __half2 h = __floats2half2_rn(v.x, v.y);
   if (p.world == 0) {
-    *reinterpret_cast<__half2*>(p.C + static_cast<size_t>(m) * p.N + n) = h;
+    *reinterpret_cast<__half2*>(out_ptr(p, m, n)) = h;
   } else if (p.mc_C != nullptr) {
     multimem_st_b32(p.mc_C + static_cast<size_t>(m) * p.ldc + p.col0 + n, *reinterpret_cast<const uint32_t*>(&h));
   } else {
@@ -662,6 +691,21 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
                 sum[i].w += v[j][i].w;
               }
           }
+          if (p.act == kActSiluGate) {
+            // lanes 0-15 hold gate columns 4l..4l+3 of the tile, lanes 16-31 the matching up columns
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float ux = __shfl_down_sync(0xffffffffu, sum[i].x, 16), uy = __shfl_down_sync(0xffffffffu, sum[i].y, 16);
+              const float uz = __shfl_down_sync(0xffffffffu, sum[i].z, 16), uw = __shfl_down_sync(0xffffffffu, sum[i].w, 16);
+              const int m = m0 + i;
+              if (lane < 16 && m < p.M) {
+                store_gate(p, m, tile, 4 * lane, sum[i].x, ux);
+                store_gate(p, m, tile, 4 * lane + 1, sum[i].y, uy);
+                store_gate(p, m, tile, 4 * lane + 2, sum[i].z, uz);
+                store_gate(p, m, tile, 4 * lane + 3, sum[i].w, uw);
+              }
+            }
+          } else
           with_act(p.act, [&](auto tag) {
             constexpr int ACT = decltype(tag)::value;
 #pragma unroll

@@ -117,4 +117,34 @@ __global__ void __launch_bounds__(kQuantThreads) fg_quantize_rows_w4_kernel(cons
   }
 }
 
+// ---- one-time weight repacking ---------------------------------------------------------------
+// B[K, N] -> W[N, K] (fp16): 64 x 64 tiles through shared memory, coalesced on both sides.  For
+// callers of the KxN operators that can afford a one-time repack: the NxK kernels are faster.
+__global__ void __launch_bounds__(256) fg_transpose_kn_to_nk_kernel(const __half* __restrict__ B, __half* __restrict__ W,
+                                                                    int N, int K) {
+  __shared__ __half tile[64][66];  // two halves of padding: conflict-free column reads
+  const int n0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int r = ty; r < 64; r += 8) {
+    const __half2 v = *reinterpret_cast<const __half2*>(B + static_cast<size_t>(k0 + r) * N + n0 + 2 * tx);
+    tile[r][2 * tx] = __low2half(v);
+    tile[r][2 * tx + 1] = __high2half(v);
+  }
+  __syncthreads();
+  for (int r = ty; r < 64; r += 8)
+    *reinterpret_cast<__half2*>(W + static_cast<size_t>(n0 + r) * K + k0 + 2 * tx) =
+        __halves2half2(tile[2 * tx][r], tile[2 * tx + 1][r]);
+}
+
+// Gate and up projection weights Wg[N, K], Wu[N, K] -> Wgu[2N, K] in which every 128 rows hold 64
+// gate rows followed by the matching 64 up rows: the layout the SiLU-gate epilogue reads.
+// blockIdx.y = destination block of 64 rows; even blocks come from Wg, odd ones from Wu.
+__global__ void __launch_bounds__(256) fg_interleave_gate_up_kernel(const uint4* __restrict__ Wg, const uint4* __restrict__ Wu,
+                                                                    uint4* __restrict__ Wgu, int chunks16) {
+  const int blk = blockIdx.y;
+  const uint4* src = ((blk & 1) ? Wu : Wg) + static_cast<size_t>(blk >> 1) * chunks16;
+  uint4* dst = Wgu + static_cast<size_t>(blk) * chunks16;
+  for (int i = blockIdx.x * 1024 + threadIdx.x; i < chunks16 && i < (blockIdx.x + 1) * 1024; i += 256) dst[i] = src[i];
+}
+
 }  // namespace fg

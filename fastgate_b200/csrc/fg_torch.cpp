@@ -220,15 +220,19 @@ int64_t workspace_status(int64_t device) {
 
 // Linear layer with a fused epilogue: C = act(x . W^T * scales + bias) + residual.
 // layout "nk": W[N,K] (fp16, or int8 with optional scales); "kn": W[K,N] fp16.
+// act "silu_gate": W is the interleaved gate/up weight of prepack_gate_up, C and residual are [M, N/2].
+// C2, C3: the output columns are split over C, C2 and C3 in that order (their widths add up to N).
 void linear_fused(at::Tensor x, at::Tensor W, at::Tensor C, c10::optional<at::Tensor> scales,
                   c10::optional<at::Tensor> bias, c10::optional<at::Tensor> residual, const std::string& act,
-                  const std::string& layout) {
+                  const std::string& layout, c10::optional<at::Tensor> C2, c10::optional<at::Tensor> C3) {
   int act_code;
   if (act == "none") act_code = FG_ACT_NONE;
   else if (act == "gelu" || act == "gelu_erf") act_code = FG_ACT_GELU_ERF;
   else if (act == "gelu_tanh") act_code = FG_ACT_GELU_TANH;
   else if (act == "silu") act_code = FG_ACT_SILU;
-  else throw std::invalid_argument("fastgate_b200: act must be none, gelu, gelu_tanh or silu");
+  else if (act == "silu_gate") act_code = FG_ACT_SILU_GATE;
+  else throw std::invalid_argument("fastgate_b200: act must be none, gelu, gelu_tanh, silu or silu_gate");
+  const bool gate = act_code == FG_ACT_SILU_GATE;
   if (layout != "nk" && layout != "kn") throw std::invalid_argument("fastgate_b200: layout must be nk or kn");
   const bool int8w = W.scalar_type() == at::kChar;
   if (int8w && layout == "kn") throw std::invalid_argument("fastgate_b200: int8 weights are stored NxK");
@@ -240,8 +244,26 @@ void linear_fused(at::Tensor x, at::Tensor W, at::Tensor C, c10::optional<at::Te
   const int64_t M = x.size(0), K = x.size(1);
   const int64_t N = (op == FG_OP_F16_KN) ? W.size(1) : W.size(0);
   if (((op == FG_OP_F16_KN) ? W.size(0) : W.size(1)) != K) throw std::runtime_error("fastgate_b200: activation and weight disagree on K");
-  if (C.numel() != M * N) throw std::runtime_error("fastgate_b200: output must hold M*N elements");
-  fg_epilogue_t ep = {nullptr, nullptr, act_code};
+  if (gate && (layout != "nk" || int8w)) throw std::invalid_argument("fastgate_b200: silu_gate takes fp16 NxK weights (prepack_gate_up)");
+  const int64_t n_out = gate ? N / 2 : N;  // columns of the result
+  fg_epilogue_t ep = {nullptr, nullptr, act_code, 0, 0, nullptr, nullptr};
+  const bool has2 = C2.has_value() && C2->defined(), has3 = C3.has_value() && C3->defined();
+  if (has2 || has3) {
+    if (gate) throw std::invalid_argument("fastgate_b200: silu_gate writes one output");
+    if (!has2) throw std::invalid_argument("fastgate_b200: C3 without C2");
+    check_tensor(*C2, "output C2", at::kHalf);
+    if (has3) check_tensor(*C3, "output C3", at::kHalf);
+    if (M > 0 && (C.numel() % M || C2->numel() % M || (has3 && C3->numel() % M)))
+      throw std::runtime_error("fastgate_b200: split outputs must hold M rows each");
+    const int64_t n1 = M > 0 ? C.numel() / M : 0, n2 = M > 0 ? C2->numel() / M : 0, n3 = (has3 && M > 0) ? C3->numel() / M : 0;
+    if (M > 0 && n1 + n2 + n3 != N) throw std::runtime_error("fastgate_b200: widths of the split outputs must add up to N");
+    ep.split1 = static_cast<int>(n1);
+    ep.split2 = static_cast<int>(n1 + n2);
+    ep.C2 = C2->data_ptr();
+    ep.C3 = has3 ? C3->data_ptr() : nullptr;
+  } else if (C.numel() != M * n_out) {
+    throw std::runtime_error("fastgate_b200: output must hold M*N elements (M*N/2 with silu_gate)");
+  }
   const void* sp = nullptr;
   if (scales.has_value() && scales->defined()) {
     if (!int8w) throw std::runtime_error("fastgate_b200: scales only apply to int8 weights");
@@ -256,7 +278,7 @@ void linear_fused(at::Tensor x, at::Tensor W, at::Tensor C, c10::optional<at::Te
   }
   if (residual.has_value() && residual->defined()) {
     check_tensor(*residual, "residual", at::kHalf);
-    if (residual->numel() != M * N) throw std::runtime_error("fastgate_b200: residual must hold M*N elements");
+    if (residual->numel() != M * n_out) throw std::runtime_error("fastgate_b200: residual must hold as many elements as the output");
     ep.residual = residual->data_ptr();
   }
   if (M == 0) return;
@@ -271,6 +293,35 @@ void linear_fused(at::Tensor x, at::Tensor W, at::Tensor C, c10::optional<at::Te
                        reinterpret_cast<fg_stream_t>(stream));
   }
   if (st != FG_OK) raise(st, op != FG_OP_F16_KN);
+}
+
+// B[K,N] fp16 -> W[N,K] fp16.
+at::Tensor prepack_kn_to_nk(at::Tensor B) {
+  check_tensor(B, "weight", at::kHalf);
+  if (B.dim() != 2 || (B.size(0) % 64) != 0 || (B.size(1) % 64) != 0)
+    throw std::invalid_argument("fastgate_b200: weight [K,N] with K and N multiples of 64 expected");
+  const c10::cuda::CUDAGuard guard(B.device());
+  at::Tensor W = at::empty({B.size(1), B.size(0)}, B.options());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(B.get_device()).stream();
+  const int st = fg_prepack_kn_to_nk(B.data_ptr(), W.data_ptr(), static_cast<int>(B.size(1)), static_cast<int>(B.size(0)),
+                                     reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+  return W;
+}
+
+// Wg[N,K], Wu[N,K] fp16 -> Wgu[2N,K] fp16, blocks of 64 rows interleaved (gate first).
+at::Tensor prepack_gate_up(at::Tensor Wg, at::Tensor Wu) {
+  check_tensor(Wg, "gate weight", at::kHalf);
+  check_tensor(Wu, "up weight", at::kHalf);
+  if (Wg.dim() != 2 || Wg.sizes() != Wu.sizes() || (Wg.size(0) % 64) != 0 || (Wg.size(1) % 128) != 0)
+    throw std::invalid_argument("fastgate_b200: gate and up weights [N,K] of one shape, N % 64 == 0, K % 128 == 0 expected");
+  const c10::cuda::CUDAGuard guard(Wg.device());
+  at::Tensor Wgu = at::empty({2 * Wg.size(0), Wg.size(1)}, Wg.options());
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(Wg.get_device()).stream();
+  const int st = fg_prepack_gate_up(Wg.data_ptr(), Wu.data_ptr(), Wgu.data_ptr(), static_cast<int>(Wg.size(0)),
+                                    static_cast<int>(Wg.size(1)), reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+  return Wgu;
 }
 
 // W[N,K] fp16 -> (W8[N,K] int8, scales[N] fp16), one scale per output channel.
@@ -354,9 +405,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("mc_c_ptr") = 0, py::arg("mc_flag_ptr") = 0);
   m.def("push_wait", &push_wait, py::arg("flag_ptr"), py::arg("world"), py::arg("target"), py::arg("device"));
   m.def("workspace_status", &workspace_status, py::arg("device"));
+  m.def("prepack_kn_to_nk", &prepack_kn_to_nk, py::arg("B"), "B[K,N] fp16 -> W[N,K] fp16 (one-time repack for the NxK operators)");
+  m.def("prepack_gate_up", &prepack_gate_up, py::arg("Wg"), py::arg("Wu"),
+        "Wg[N,K], Wu[N,K] fp16 -> Wgu[2N,K]: 64 gate rows, then the matching 64 up rows, per 128 rows (for act='silu_gate')");
   m.def("linear_fused", &linear_fused, py::arg("x"), py::arg("W"), py::arg("C"), py::arg("scales") = py::none(),
         py::arg("bias") = py::none(), py::arg("residual") = py::none(), py::arg("act") = "none", py::arg("layout") = "nk",
-        "C = act(x . W^T * scales + bias) + residual in one kernel (fp32 until the final rounding)");
+        py::arg("C2") = py::none(), py::arg("C3") = py::none(),
+        "C = act(x . W^T * scales + bias) + residual in one kernel (fp32 until the final rounding); act='silu_gate': "
+        "C[M,N/2] = silu(x.Wgate^T) * (x.Wup^T) on a weight from prepack_gate_up; C2/C3: the output columns are split over "
+        "C, C2, C3 (a fused QKV projection written into three tensors)");
   m.def("fastgemv_int4", &op_wfirst_int4, py::arg("W4"), py::arg("x"), py::arg("C"), py::arg("scales") = py::none(),
         py::arg("zero_point") = 8,
         "C[M,N] = sum_g scales[n,g] * sum_k x[m,k] * (w4[n,k] - zero_point): W4 [N,K/2] uint8, low nibble = even k");

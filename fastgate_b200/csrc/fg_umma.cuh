@@ -25,6 +25,7 @@ constexpr int kUmmaThreads = (6 + 2 * 4) * 32;             // two finisher teams
 constexpr int kUmmaGroupThreads = (6 + kUmmaMT / 4) * 32;  // grouped and chained kernels: one team
 constexpr int kUmmaChains = 2;         // independent accumulation chains per tile (summed in the epilogue)
 constexpr uint32_t kTmemCols = 64;     // 2 buffers x 2 chains x 16 columns (16-row kernels)
+constexpr uint32_t kGateXchBytes = 16 * kTileN * 4;  // SiLU gate: the epilogue's swap buffer
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
@@ -101,7 +102,7 @@ __device__ __forceinline__ void store_out1(const KParams& p, int m, int n, float
   if (ACT != kActNone || p.bias != nullptr || p.residual != nullptr) v = epilogue1<ACT>(p, m, n, v);
   const __half h = __float2half_rn(v);
   if (p.world == 0) {
-    p.C[static_cast<size_t>(m) * p.N + n] = h;
+    *out_ptr(p, m, n) = h;
   } else if (p.mc_C != nullptr) {
     // multicast stores are at least 32 bits wide: even lanes store their column and the next one
     // (called by whole warps with a uniform m: lane = column within the tile)
@@ -142,9 +143,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
   const uint32_t tmem_slot = bar_flush + 16;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + 16 * S + 48);
   volatile uint32_t* prev_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + ring_bytes + 16 * S + 52);  // [2]
+  // SiLU gate: 16 x 128 floats through which the epilogue warps swap gate and up sums
+  float* gate_xch = reinterpret_cast<float*>(smem_gen + ring_bytes + 16 * S + 64);
+  const bool gated = (p.act == kActSiluGate);
 
   // refuse a launch that does not fit the parameters (see fg_streamk_kernel)
-  if (blockDim.x != static_cast<unsigned>(kUmmaThreads) || dynamic_smem_size() < 1023u + ring_bytes + 16u * S + 64u) {
+  if (blockDim.x != static_cast<unsigned>(kUmmaThreads) ||
+      dynamic_smem_size() < 1023u + ring_bytes + 16u * S + 64u + (gated ? kGateXchBytes : 0u)) {
     if (threadIdx.x == 0) atomicExch(p.status, kStatusBadLaunch);
     return;
   }
@@ -326,7 +331,20 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
           trace[7] = globaltimer_ns();  // accumulator read back
           trace[11] += trace[7] - te0;  // waiting for it
         }
-        if (whole) {
+        if (whole && gated) {
+          // warps 0-1 hold the gate rows of the tile, warps 2-3 the up rows: swap through shared
+          // memory (every epilogue thread takes both barriers, whatever its own state)
+#pragma unroll
+          for (int m = 0; m < 16; ++m) gate_xch[m * kTileN + n_in_tile] = __uint_as_float(r[m]);
+          named_bar_sync(1, 128);
+          if (n_in_tile < 64) {
+#pragma unroll
+            for (int m = 0; m < 16; ++m)
+              if (mg * 16 + m < p.M)
+                store_gate(p, mg * 16 + m, tile, n_in_tile, __uint_as_float(r[m]), gate_xch[m * kTileN + 64 + n_in_tile]);
+          }
+          named_bar_sync(1, 128);
+        } else if (whole) {
           with_act(p.act, [&](auto tag) {
             constexpr int ACT = decltype(tag)::value;
 #pragma unroll

@@ -304,14 +304,36 @@ void fg_chain_destroy(fg_chain_t* chain);
  *     C = act(x . W^T * scale + bias[n]) + residual[m, n]
  * evaluated in fp32 and rounded once.  Any of bias, residual may be NULL; ep == NULL is the
  * plain product.  op = FG_OP_*; scales only for FG_OP_W8A16_NK. */
-enum { FG_ACT_NONE = 0, FG_ACT_GELU_ERF = 1, FG_ACT_GELU_TANH = 2, FG_ACT_SILU = 3 };
+enum { FG_ACT_NONE = 0, FG_ACT_GELU_ERF = 1, FG_ACT_GELU_TANH = 2, FG_ACT_SILU = 3, FG_ACT_SILU_GATE = 4 };
 typedef struct fg_epilogue_t {
   const void* bias;      /* [N] fp16 */
-  const void* residual;  /* [M, N] fp16, added after the activation */
+  const void* residual;  /* [M, N] fp16 (row length = that of the output), added after the activation */
   int act;               /* FG_ACT_* */
+  /* Output split (a fused QKV projection written straight into the consumer's three tensors):
+   * with split1 > 0, columns [0, split1) go to C, [split1, split2) to C2 and [split2, N) to C3, each
+   * a dense row-major tensor of its own width.  split1, split2 multiples of 8; split2 == N: two
+   * outputs; all zero: one output. */
+  int split1, split2;
+  void* C2;
+  void* C3;
 } fg_epilogue_t;
+/* FG_ACT_SILU_GATE (gated MLP, op FG_OP_F16_NK only): W is the [N, K] weight made by fg_prepack_gate_up
+ * from a gate and an up projection of N/2 rows each; C and residual are [M, N/2], bias (optional) is
+ * [N] in the order of W's rows:
+ *     C[m, j] = silu(x . Wgate[j] + bias_gate[j]) * (x . Wup[j] + bias_up[j]) + residual[m, j]
+ * One pass over both projections, no intermediate tensors. */
 int fg_gemm_fused(int op, const void* x, const void* W, const void* scales, void* C, int M, int N, int K,
                   const fg_epilogue_t* ep, void* ws, size_t ws_bytes, fg_stream_t stream);
+
+/* ---- one-time weight repacking ------------------------------------------------------------
+ * fg_prepack_kn_to_nk: B[K, N] -> W[N, K] (fp16, N and K multiples of 64).  Callers of the KxN
+ * operators (edgemm_m8n128k64x4, flat_gemm_*) whose weight is fixed can repack it once and use the
+ * NxK entry points from then on.  The reference only sketches packed weight containers
+ * (backend/cuda/hk/utility.cuh:13-46) and has no repacking routine.
+ * fg_prepack_gate_up: Wg[Nh, K], Wu[Nh, K] -> Wgu[2 Nh, K] whose every 128 rows hold 64 gate rows
+ * followed by the matching 64 up rows (Nh a multiple of 64): the weight FG_ACT_SILU_GATE takes. */
+int fg_prepack_kn_to_nk(const void* B, void* W, int N, int K, fg_stream_t stream);
+int fg_prepack_gate_up(const void* Wg, const void* Wu, void* Wgu, int Nh, int K, fg_stream_t stream);
 
 /* ---- int8 weight producer ----------------------------------------------------------------
  * Per-output-channel symmetric quantiser for fg_gemm_w8a16_nk: W[N,K] fp16 -> W8[N,K] int8

@@ -167,6 +167,30 @@ def epilogue(C32, bias=None, residual=None, act: int = 0) -> np.ndarray:
     return out
 
 
+def silu_gate(G32, U32, bias_gate=None, bias_up=None, residual=None) -> np.ndarray:
+    """silu(G32 + bias_gate) * (U32 + bias_up) + residual in fp32: the gated-MLP epilogue, which has no
+    counterpart in the reference (its operators stop at the matrix product); G32 and U32 are the
+    fp32-accumulated products of the gate and the up projection."""
+    g = np.asarray(G32, np.float32).copy()
+    u = np.asarray(U32, np.float32).copy()
+    if bias_gate is not None:
+        g += _h(bias_gate).astype(np.float32).reshape(1, -1)
+    if bias_up is not None:
+        u += _h(bias_up).astype(np.float32).reshape(1, -1)
+    out = (g / (np.float32(1) + np.exp(-g, dtype=np.float32))) * u
+    if residual is not None:
+        out = out + _h(residual).astype(np.float32)
+    return out.astype(np.float32)
+
+
+def interleave_gate_up(Wg, Wu) -> np.ndarray:
+    """The weight layout the gated epilogue reads: per 128 rows, 64 gate rows then the matching 64 up rows."""
+    Wg, Wu = np.asarray(Wg), np.asarray(Wu)
+    n, k = Wg.shape
+    assert Wu.shape == (n, k) and n % 64 == 0
+    return np.stack([Wg.reshape(n // 64, 64, k), Wu.reshape(n // 64, 64, k)], axis=1).reshape(2 * n, k)
+
+
 def gemm_w4a16_nk(x, W4, scales=None, zero_point: int = 8) -> np.ndarray:
     """C32[M,N] = sum_g scales[n,g] * sum_{k in g} x[m,k] * (nibble[n,k] - zero_point); scales is
     [N] / [N,1] (per channel), [N, K/128] (group-wise) or None (1)."""
