@@ -580,21 +580,27 @@ def run_ours(args):
             push_sets[slot] = [shard.PushBuffers(16, 8192 * world, dev) for _ in cases]
         return push_sets[slot]
 
-    def step_push(slot=0, inputs=None, sink=None):
-        # The five calls are chained the way the layers of a model are: call i+1 reads its
-        # activations only after every rank's tiles of call i have landed here (a wait inside
-        # the kernel, after its first weight tiles are already on their way); one wait kernel
-        # closes the step, so all five outputs are complete on every rank when the step ends.
+    def step_push(slot=0, inputs=None, sink=None, chained=False):
+        # Five calls whose tiles go straight into every rank's output; wait kernels close the step, so
+        # all five outputs are complete on every rank when the step ends.  As at N = 1 the calls do not
+        # read each other's results, so a call only follows its predecessor in stream order.
+        # chained=True: the calls are tied the way the layers of a model are: call i+1 reads its
+        # activations only after every rank's tiles of call i have landed here (a wait inside the
+        # kernel, after its first weight tiles are already on their way).
         # Each call of a step pushes into buffers of its own, each step in flight into a set of its own.
         bufs = push_set(slot)
         prev = None
         for ci in range(len(cases)):
             lay = layers[(state["i"] + ci) % N_WEIGHT_COPIES]
-            res = lay.forward_push((inputs or xs)[ci], wait=False, after=prev, into=bufs[ci])
+            res = lay.forward_push((inputs or xs)[ci], wait=False, after=prev if chained else None, into=bufs[ci])
             prev = bufs[ci]
             if sink is not None:
                 sink.append((ci, res, prev))
-        lay.push_wait(prev)
+        if chained:
+            lay.push_wait(prev)  # the last call's counters imply the earlier ones'
+        else:
+            for pb in bufs:
+                lay.push_wait(pb)
         state["i"] += 1
 
     # ---- device-resident timing -------------------------------------------------------
@@ -621,7 +627,7 @@ def run_ours(args):
         batches_local = time_batches(step_local, args.steps, args.warmup, world, stream)
         launches = N_BATCHES * args.steps * len(cases)
     ms_local = statistics.median(batches_local)
-    batches_full, batches_nccl = batches_local, None
+    batches_full, batches_nccl, batches_chained = batches_local, None, None
     gather_kind = "none (single GPU)"
     push_checked = None
     if world > 1:
@@ -652,8 +658,10 @@ def run_ours(args):
                     push_checked = bool(t.item())
                     torch.cuda.synchronize()
                 batches_full = time_batches(step_push, args.steps, args.warmup, world, stream)
-                launches = N_BATCHES * args.steps * (len(cases) + 1)  # five compute kernels and the closing wait kernel
-                gather_kind = "fused: epilogue stores tiles into every rank's C over NVLink + bounded flag wait"
+                launches = N_BATCHES * args.steps * 2 * len(cases)  # five compute kernels and five wait kernels
+                gather_kind = ("fused: the epilogue stores every tile into every rank's C over NVLink; bounded waits on the "
+                               "arrival counters close the step")
+                batches_chained = time_batches(lambda: step_push(chained=True), args.steps, args.warmup, world, stream)
             except Exception as e:  # symmetric memory unavailable: keep the NCCL number
                 sys.stderr.write(f"rank {rank}: fused all-gather unavailable ({e}); reporting the NCCL path\n")
     ms_full = statistics.median(batches_full)
@@ -786,6 +794,11 @@ def run_ours(args):
     }
     if world > 1:
         line["push_checked"] = push_checked
+        if batches_chained is not None:
+            ms_c = statistics.median(batches_chained) / args.steps
+            line["push_chained"] = {"value": bytes_step_rank * world / ms_c / 1e6, "unit": "GB/s", "ms_per_step": ms_c,
+                                    "what": "the five calls tied like dependent layers: each reads its activations only after "
+                                            "every rank's tiles of the previous call have arrived (in-kernel wait)"}
     if configs is not None:
         line["configs"] = configs
     if dit is not None:

@@ -1214,6 +1214,31 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   return FG_OK;
 }
 
+int fg_noalloc_status(int* status_out, fg_stream_t stream) {
+  if (status_out == nullptr) return FG_ERR_NULL;
+  DeviceInfo* dev = nullptr;
+  int st = device_info(&dev);
+  if (st != FG_OK) return st;
+  int dev_index = 0;
+  cudaError_t e = cudaGetDevice(&dev_index);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  unsigned char* scratch = nullptr;
+  if ((st = noalloc_scratch(dev_index, &scratch)) != FG_OK) return st;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int v = 0;
+  e = cudaMemcpyAsync(&v, scratch, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  *status_out = v;
+  return FG_OK;
+}
+
 const char* fg_status_str(int status) {
   switch (status) {
     case FG_OK: return "ok";

@@ -166,6 +166,10 @@ int fg_quantize_rows_w4(const void* W, uint8_t* W4, void* scales, int groups, in
  * fp16 atomics on C instead of scratch (backend/cuda/hk/edgemm.cu:138-142). */
 int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, int K,
                            fg_stream_t stream);
+/* Synchronises `stream` and copies the status word that the last fg_gemm_f16_nk_noalloc call on the
+ * current device left in the built-in scratch (FG_OK, FG_ERR_TIMEOUT or FG_ERR_PLAN) to *status_out.
+ * The next call clears the word itself.  Allocates nothing; no counterpart in the reference. */
+int fg_noalloc_status(int* status_out, fg_stream_t stream);
 
 /* The fp16 and int8 operations with an explicit plan (from fg_plan, possibly edited):
  * used by the tuner and the tests that walk every plan the heuristic can emit.  int4 plans

@@ -47,6 +47,8 @@ def test_noalloc_matches_workspace_entry_point_twice(M, N, K):
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"round {round_}: bits differ"
         # and both agree with the CPU oracle
         oracle.check_tolerance(got.cpu().numpy(), oracle.gemm_nk(x.cpu().numpy(), W.cpu().numpy()), "oracle")
+        v = ctypes.c_int(-1)
+        assert L.fg_noalloc_status(ctypes.byref(v), _stream()) == capi.FG_OK and v.value == capi.FG_OK
 
 
 def test_noalloc_more_than_16_rows_runs_in_16_row_passes():
