@@ -1155,7 +1155,7 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   const int sms = dev->sm_count < kNoAllocMaxGrid ? dev->sm_count : kNoAllocMaxGrid;
   // The built-in scratch holds 16-row partial tiles: plan (and run) in passes of at most 16 rows.
   if ((st = fg_plan_tiled(FG_OP_F16_NK, M < 16 ? M : 16, N, K, sms, dev->smem_optin, &pl)) != FG_OK) return st;
-  if (pl.grid > kNoAllocMaxGrid || pl.m_tile > 16 || pl.math == 4) return FG_ERR_WORKSPACE;
+  if (pl.grid > kNoAllocMaxGrid || pl.m_tile > 16 || pl.math >= 4) return FG_ERR_WORKSPACE;
   pl.pdl = 0;  // a memset precedes every launch, so there is no kernel to overlap with
 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

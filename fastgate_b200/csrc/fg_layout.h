@@ -39,6 +39,7 @@ static inline int fg_smem_bytes(int op, int m_tile, int chunks, int stages, int 
 
 /* row-split GEMV kernel (math 4): x, ring of whole-row stages, cross-warp sums, stage table, barriers */
 #define FG_GEMV_MAX_M 2
+#define FG_GEMV_M2_MAX_ELEMS (48LL << 20) /* two rows: only up to this many weights (96 MB) */
 #define FG_GEMV_MAX_OUT 8                /* rows per stage x token rows */
 #define FG_GEMV_MAX_WARPS 12             /* consumer warps; each owns every warps-th stage */
 #define FG_GEMV_MIN_K 1024

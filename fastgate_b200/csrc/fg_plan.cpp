@@ -97,7 +97,10 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
   if (sm_count <= 0) sm_count = 148;                 // B200
   if (smem_optin_bytes <= 0) smem_optin_bytes = 232448;  // 227 KB opt-in per CTA on sm_100
 
-  if (allow_gemv && gemv_eligible(op, M, K)) {
+  // Two rows: the GEMV kernel wins on every shape measured up to 96 MB of weights (11008 x 4096: 17.0 us
+  // against 17.8 tiled; 3072 x 12288: 17.7 / 18.1; 9216 x 3072: 12.3 / 12.8) and ties at 8192 x 8192
+  // (24.1 / 24.0), where a step that alternates it with tiled calls loses 0.6 us per call.
+  if (allow_gemv && gemv_eligible(op, M, K) && (M == 1 || static_cast<long long>(N) * K <= FG_GEMV_M2_MAX_ELEMS)) {
     const int st = plan_gemv(op, M, N, K, sm_count, smem_optin_bytes, out);
     if (st == FG_OK) return st;  // no room for a ring: fall through to the tiled kernels
   }
