@@ -221,7 +221,7 @@ def spread(ms_list, per: float) -> dict:
 
 
 def pipelined_e2e(compute, x_all_host, n_rows: int, n_cols: int, dev, stream, steps: int, warmup: int, world: int = 1,
-                  read_out=None) -> float:
+                  read_out=None, prepare=None) -> float:
     """ms for `steps` end-to-end steps on this rank's GPU, two steps deep, max over ranks.
 
     Every step copies its activations from pinned host memory (side stream), runs
@@ -230,7 +230,8 @@ def pipelined_e2e(compute, x_all_host, n_rows: int, n_cols: int, dev, stream, st
     flight, as a serving loop does.  All copies of all timed steps lie inside the timed
     region, which ends when the last step's results are in host memory.  `read_out(out_dev, k)`
     (optional) moves a step's results into out_dev on `stream` when `compute` leaves them
-    elsewhere."""
+    elsewhere.  `prepare(x_dev, out_dev)` (optional) sees the two sets of device buffers before the
+    first step (to capture graphs over them)."""
     import torch
 
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
@@ -241,6 +242,8 @@ def pipelined_e2e(compute, x_all_host, n_rows: int, n_cols: int, dev, stream, st
     ev_comp = [torch.cuda.Event() for _ in range(2)]
     ev_out = [torch.cuda.Event() for _ in range(2)]
     counter = {"k": 0}
+    if prepare is not None:
+        prepare(x_dev, out_dev)
 
     def run(n: int) -> int:
         last = 0
@@ -335,7 +338,7 @@ def graph_of(step_fn, stream, use_graph: bool, warm: int = 2):
         if not use_graph:
             return None
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=stream):
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
             step_fn()
     return g
 
@@ -485,15 +488,25 @@ def dit_sharded(args, world: int, rank: int, local: int, dev, stream) -> dict:
                        f"{sum(c.weight_bytes for c in cases_all) / 1e9:.2f} GB, N-sharded over {world} GPUs", "scaling": "strong",
            "steps": steps}
 
-    def leg(name, fn, what):
+    def leg(name, fn, what, graphed=True):
+        # Legs made of this library's kernels only are captured once (one pass) and replayed, as the
+        # single-GPU configurations are; the NCCL leg is launched from the host call by call.
         try:
+            graph = None
             with torch.cuda.stream(stream):
                 fn()
                 torch.cuda.synchronize()
-            ms = time_batches(fn, steps, warm, world, stream, batches=3)
+                if graphed and not args.no_graph:
+                    barrier_sync(world)
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                        fn()
+            ms = time_batches(fn, steps, warm, world, stream, graph=graph, batches=3)
             s = spread(ms, steps)
             res[name] = {"ms_per_pass": s["median"], "ms_min": s["min"], "ms_max": s["max"],
-                         "value": bytes_pass / s["median"] / 1e6, "unit": "GB/s", "what": what}
+                         "value": bytes_pass / s["median"] / 1e6, "unit": "GB/s", "what": what,
+                         "launch": "cuda graph replay" if graph is not None else "stream launches"}
+            del graph
         except Exception as e:
             res[name] = {"unavailable": str(e)}
 
@@ -513,7 +526,7 @@ def dit_sharded(args, world: int, rank: int, local: int, dev, stream) -> dict:
         lay.push_wait(prev)
 
     leg("no_gather", step_local, "every rank computes its output slices, nothing is assembled")
-    leg("nccl_gather", step_nccl, "all_gather_into_tensor + [g,M,N/g]->[M,N] copy after every linear")
+    leg("nccl_gather", step_nccl, "all_gather_into_tensor + [g,M,N/g]->[M,N] copy after every linear", graphed=False)
     if not args.no_push:
         leg("push_per_linear", step_push, "tiles stored into every rank's output from the kernel's epilogue; each linear waits "
                                           "in-kernel for the previous one's tiles from all ranks")
@@ -525,12 +538,11 @@ def dit_sharded(args, world: int, rank: int, local: int, dev, stream) -> dict:
             grp = LinearGroup([xs[i % 4] for i in range(len(layers))], [lay.w for lay in layers], None,
                               peer_C_ptrs=[pb.c_ptrs for pb in pbs], flag_ptrs=gflag.flag_ptrs, rank=rank,
                               n_totals=[lay.n_total for lay in layers], mc_C_ptrs=[pb.mc_out for pb in pbs],
-                              mc_flag_ptr=gflag.mc_flag)
+                              mc_flag_ptr=gflag.mc_flag, target_dev_ptr=gflag.target_ptr)
 
             def step_group():
                 grp.run()
-                gflag.target += grp.tiles
-                fg.push_wait(gflag.flag_ptrs[rank], world, gflag.target, local)
+                fg.push_wait_dev(gflag.flag_ptrs[rank], world, gflag.target_ptr, local)
 
             leg("push_grouped", step_group, "the whole stack as one grouped launch per pass, tiles pushed into every rank's "
                                             "outputs, one wait" + (", multimem" if gflag.mc_flag else ""))
@@ -604,28 +616,32 @@ def run_ours(args):
         state["i"] += 1
 
     # ---- device-resident timing -------------------------------------------------------
-    graph = None
-    use_graph = (not args.no_graph) and world == 1
-    with torch.cuda.stream(stream):
-        for _ in range(3):
-            step_local()
-        torch.cuda.synchronize()
-        if use_graph:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for _ in range(N_WEIGHT_COPIES):  # every rotation of the copies
-                    step_local()
+    use_graph = not args.no_graph
+    # one replay = N_WEIGHT_COPIES steps (every rotation of the weight copies)
+    reps = max(1, -(-args.steps // N_WEIGHT_COPIES))
+    wreps = max(1, -(-args.warmup // N_WEIGHT_COPIES))
+
+    def timed(step_fn):
+        """(ms per `args.steps` steps for each batch, the graph or None, steps actually run per batch).
+        Legs made of this library's kernels only are captured once and replayed at every N (the fused
+        path keeps its tile totals on the device, so nothing in a launch changes between replays)."""
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                step_fn()
+            torch.cuda.synchronize()
+            if not use_graph:
+                return time_batches(step_fn, args.steps, args.warmup, world, stream), None, args.steps
+            barrier_sync(world)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                for _ in range(N_WEIGHT_COPIES):
+                    step_fn()
+        ran = reps * N_WEIGHT_COPIES
+        return [ms * args.steps / ran for ms in time_batches(None, reps, wreps, world, stream, graph=g)], g, ran
 
     sampler = ClockSampler(local) if rank == 0 else None
-    if graph is not None:
-        # one replay = N_WEIGHT_COPIES steps
-        reps = max(1, -(-args.steps // N_WEIGHT_COPIES))
-        wreps = max(1, -(-args.warmup // N_WEIGHT_COPIES))
-        batches_local = [ms * args.steps / (reps * N_WEIGHT_COPIES) for ms in time_batches(None, reps, wreps, world, stream, graph=graph)]
-        launches = N_BATCHES * reps * N_WEIGHT_COPIES * len(cases)
-    else:
-        batches_local = time_batches(step_local, args.steps, args.warmup, world, stream)
-        launches = N_BATCHES * args.steps * len(cases)
+    batches_local, graph, ran_steps = timed(step_local)
+    launches = N_BATCHES * ran_steps * len(cases)
     ms_local = statistics.median(batches_local)
     batches_full, batches_nccl, batches_chained = batches_local, None, None
     gather_kind = "none (single GPU)"
@@ -657,11 +673,18 @@ def run_ours(args):
                     dist.all_reduce(t, op=dist.ReduceOp.MIN)
                     push_checked = bool(t.item())
                     torch.cuda.synchronize()
-                batches_full = time_batches(step_push, args.steps, args.warmup, world, stream)
-                launches = N_BATCHES * args.steps * 2 * len(cases)  # five compute kernels and five wait kernels
+                batches_full, graph_push, ran_steps = timed(step_push)
+                launches = N_BATCHES * ran_steps * 2 * len(cases)  # five compute kernels and five wait kernels
                 gather_kind = ("fused: the epilogue stores every tile into every rank's C over NVLink; bounded waits on the "
                                "arrival counters close the step")
-                batches_chained = time_batches(lambda: step_push(chained=True), args.steps, args.warmup, world, stream)
+                batches_chained, graph_chained, _ = timed(lambda: step_push(chained=True))
+                with torch.cuda.stream(stream):
+                    torch.cuda.synchronize()
+                    ok = fg.workspace_status(local) == 0  # no wait of the replayed steps gave up
+                    t = torch.tensor([1 if ok else 0], device=dev)
+                    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                    push_checked = push_checked and bool(t.item())
+                    torch.cuda.synchronize()
             except Exception as e:  # symmetric memory unavailable: keep the NCCL number
                 sys.stderr.write(f"rank {rank}: fused all-gather unavailable ({e}); reporting the NCCL path\n")
     ms_full = statistics.median(batches_full)
@@ -722,24 +745,51 @@ def run_ours(args):
             elif use_push:
                 # Three sets of push buffers in rotation: a set is pushed into again three steps later, and
                 # no rank can get there before every rank's host has seen the results of the step that used
-                # it last (each call waits in-kernel for all ranks' tiles of the previous call, and a host
+                # it last (the waits that close a step need all ranks' tiles of that step, and a host
                 # issues step k+2 only after it holds step k's results).
-                got = []
-                step_push(slot=1 + k % 3, inputs=[x_dev[rows[ci]:rows[ci + 1]] for ci in range(len(cases))], sink=got)
-                for ci, res, _ in got:
-                    out_dev[rows[ci]:rows[ci + 1]].copy_(res)
+                if e2e_graphs:
+                    e2e_graphs[k % len(e2e_graphs)].replay()
+                else:
+                    push_step_e2e(x_dev, out_dev, k)
             else:
                 for ci in range(len(cases)):
                     res = layers[(state["i"] + ci) % N_WEIGHT_COPIES].forward(x_dev[rows[ci]:rows[ci + 1]])
                     out_dev[rows[ci]:rows[ci + 1]].copy_(res)
                 state["i"] += 1
 
+        def push_step_e2e(x_dev, out_dev, k):
+            state["i"] = k
+            got = []
+            step_push(slot=1 + k % 3, inputs=[x_dev[rows[ci]:rows[ci + 1]] for ci in range(len(cases))], sink=got)
+            for ci, res, _ in got:
+                out_dev[rows[ci]:rows[ci + 1]].copy_(res)
+
+        e2e_graphs = []
+
+        def prepare_e2e(x_devs, out_devs):
+            # The fused path's step (five pushing calls, five waits, five copies into the result block) is
+            # captured once per combination of input block (2), push-buffer set (3) and weight copy (4):
+            # twelve graphs, replayed in turn.
+            if not (use_push and use_graph):
+                return
+            with torch.cuda.stream(stream):
+                for key in range(12):
+                    push_step_e2e(x_devs[key & 1], out_devs[key & 1], key)
+                torch.cuda.synchronize()
+                barrier_sync(world)
+                for key in range(12):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream, capture_error_mode="thread_local"):
+                        push_step_e2e(x_devs[key & 1], out_devs[key & 1], key)
+                    e2e_graphs.append(g)
+
         ms_e2e = pipelined_e2e(compute_e2e, x_all_host, rows[-1], n_cols, dev, stream, args.steps,
-                               args.warmup if world == 1 else max(3, args.warmup), world)
+                               args.warmup if world == 1 else max(3, args.warmup), world, prepare=prepare_e2e)
         e2e = {"value": bytes_step_rank * world / (ms_e2e / args.steps) / 1e6, "unit": "GB/s",
                "ms_per_step": ms_e2e / args.steps,
                "how": "two steps in flight: copies on side streams, the host waits for step k-1 while step k runs"
-                      + ("; every rank copies in the step's activations and copies out the full assembled outputs" if world > 1 else ""),
+                      + ("; every rank copies in the step's activations and copies out the full assembled outputs" if world > 1 else "")
+                      + ("; a step's calls are replayed from a graph captured over the operator calls" if e2e_graphs else ""),
                "h2d_bytes_per_step": x_all_host.numel() * 2,
                "d2h_bytes_per_step": rows[-1] * n_cols * 2}
 
@@ -778,8 +828,8 @@ def run_ours(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "calls_per_step": len(cases),
                    "l2": f"{N_WEIGHT_COPIES} rotating weight copies (537 MB) > 126 MB L2",
-                   "launch": "cuda graph replay" if graph is not None else "stream launches (the fused path's wait targets grow "
-                             "with every call, so a captured graph could not be replayed)",
+                   "launch": ("cuda graph replay" if graph is not None else "stream launches")
+                             + ("; the NCCL leg is launched call by call" if world > 1 else ""),
                    "sharding": f"N-sharded, {world} x 8192 columns; gather: {gather_kind}" if world > 1 else "single GPU"},
         "batches": {"what": f"{N_BATCHES} timed regions of {args.steps} steps each; value is their median",
                     "ms_per_step": [round(b / args.steps, 6) for b in batches_full]},

@@ -199,6 +199,22 @@ int prepare_kernel(const fg_plan_t& pl, DeviceInfo* dev, KernelFn* out) {
   return FG_OK;
 }
 
+// One warp, launched so that it overlaps its neighbours in the stream (see fg_push_wait_kernel).
+template <typename... Params, typename... Args>
+cudaError_t launch_wait(void (*kern)(Params...), cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<Params>(args)...);
+}
+
 int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const CUtensorMap& tmX,
                const fg::KParams& p, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
@@ -373,7 +389,11 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   p.wait_target = 0;
   p.mc_C = nullptr;
   p.mc_flag = nullptr;
+  p.target_dev = nullptr;
+  p.wait_target_dev = nullptr;
   if (peers != nullptr) {
+    p.target_dev = peers->target_dev;
+    p.wait_target_dev = peers->wait_target_dev;
     if (peers->mc_C != nullptr && peers->mc_flag != nullptr) {
       p.mc_C = static_cast<__half*>(peers->mc_C);
       p.mc_flag = peers->mc_flag;
@@ -564,6 +584,8 @@ int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, 
     if (!aligned16(peers->C[q]) || (reinterpret_cast<uintptr_t>(peers->flag[q]) & 7u) != 0) return FG_ERR_ALIGN;
   }
   if ((reinterpret_cast<uintptr_t>(peers->wait_flags) & 7u) != 0) return FG_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(peers->target_dev) & 7u) != 0 || (reinterpret_cast<uintptr_t>(peers->wait_target_dev) & 7u) != 0)
+    return FG_ERR_ALIGN;
   if ((peers->mc_C == nullptr) != (peers->mc_flag == nullptr)) return FG_ERR_NULL;  // both multicast mappings or none
   if (!aligned16(peers->mc_C) || (reinterpret_cast<uintptr_t>(peers->mc_flag) & 7u) != 0) return FG_ERR_ALIGN;
   int st = check_common(x, W_shard, peers->C[peers->rank], M, N_local, K, ws, ws_bytes);
@@ -580,9 +602,23 @@ int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long lo
                  fg_stream_t stream) {
   if (my_flags == nullptr || ws == nullptr) return FG_ERR_NULL;
   if (world < 1 || world > fg::kMaxPeers) return FG_ERR_PLAN;
-  fg::fg_push_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(my_flags, world, target,
-                                                                              static_cast<int*>(ws));
-  const cudaError_t e = cudaGetLastError();
+  const cudaError_t e = launch_wait(fg::fg_push_wait_kernel, reinterpret_cast<cudaStream_t>(stream), my_flags, world, target,
+                                    static_cast<int*>(ws));
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
+int fg_push_wait_dev(const unsigned long long* my_flags, int world, const unsigned long long* target_dev, void* ws,
+                     fg_stream_t stream) {
+  if (my_flags == nullptr || target_dev == nullptr || ws == nullptr) return FG_ERR_NULL;
+  if (world < 1 || world > fg::kMaxPeers) return FG_ERR_PLAN;
+  if ((reinterpret_cast<uintptr_t>(target_dev) & 7u) != 0) return FG_ERR_ALIGN;
+  const cudaError_t e = launch_wait(fg::fg_push_wait_dev_kernel, reinterpret_cast<cudaStream_t>(stream), my_flags, world,
+                                    target_dev, static_cast<int*>(ws));
   if (e != cudaSuccess) {
     g_last_cuda = static_cast<int>(e);
     return FG_ERR_CUDA;
@@ -603,6 +639,7 @@ struct fg_group {
   int world, rank;
   unsigned long long* flag[8];
   unsigned long long* mc_flag;
+  unsigned long long* target_dev;
 };
 
 size_t fg_group_table_bytes(int count) {
@@ -718,6 +755,7 @@ int fg_group_create(int op, const fg_problem_t* problems, int count, const fg_pe
   for (int q = 0; q < 8; ++q) grp->flag[q] = (q < world) ? peers->flag[q] : nullptr;
   // multicast only if the flag array and every problem's output have a multicast mapping
   grp->mc_flag = (world > 0) ? peers->mc_flag : nullptr;
+  grp->target_dev = (world > 0) ? peers->target_dev : nullptr;
   for (int i = 0; i < count && grp->mc_flag != nullptr; ++i)
     if (problems[i].mc_C == nullptr || !aligned16(problems[i].mc_C)) grp->mc_flag = nullptr;
   *out = grp;
@@ -765,6 +803,8 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
   g.rank = grp->rank;
   for (int q = 0; q < 8; ++q) g.peer_flag[q] = grp->flag[q];
   g.mc_flag = grp->mc_flag;
+  g.target_dev = grp->target_dev;
+  g.total_tiles = grp->total_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grp->grid);
   cfg.blockDim = dim3(fg::kUmmaGroupThreads);

@@ -120,6 +120,12 @@ struct KParams {
   const unsigned long long* wait_flags;
   int wait_world;
   unsigned long long wait_target;
+  // The same two numbers kept on the device, so that a captured graph can be replayed: a pushing
+  // launch adds its tile count to *target_dev (this rank's running total for the buffers it pushes
+  // into), and a dependent launch reads its wait target from *wait_target_dev once the grid
+  // dependency has resolved (the launch that pushed into those buffers has added its share by then).
+  unsigned long long* target_dev;
+  const unsigned long long* wait_target_dev;
 };
 
 __host__ __device__ constexpr int chunk_bytes(int op, int mt) {
@@ -433,12 +439,16 @@ __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float
 }
 
 // One thread tells every rank that one more output tile of this rank has been delivered.
-// The callers make the tile's stores visible system-wide first (fence + barrier).
+// It is called after a barrier that all threads which stored parts of the tile have passed: one
+// release at system scope by this thread (the multicast reduction carries it; otherwise one fence
+// before the per-rank atomics) then orders all their stores before the counters, which is far
+// cheaper than a system-scope fence in each of the storing threads.
 __device__ __forceinline__ void signal_tile_delivered(const KParams& p) {
   if (p.mc_flag != nullptr) {
     multimem_red_release_add_u64(p.mc_flag + p.rank, 1ull);
     return;
   }
+  fence_acq_rel_sys();
   for (int q = 0; q < p.world; ++q) atomicAdd_system(p.peer_flag[q] + p.rank, 1ull);
 }
 
@@ -563,7 +573,12 @@ __device__ __forceinline__ void run_producer(const CUtensorMap& tmW, const CUten
     }
   }
   griddep_wait();
-  if (p.wait_flags != nullptr && !wait_counters(p.wait_flags, p.wait_world, p.wait_target)) {
+  // after the wait: every earlier launch of the stream, including one that still compared these
+  // buffers' counters with the old total, has completed
+  if (blockIdx.x == 0 && p.target_dev != nullptr) atomicAdd(p.target_dev, static_cast<unsigned long long>(p.tiles));
+  unsigned long long wait_target = p.wait_target;
+  if (p.wait_flags != nullptr && p.wait_target_dev != nullptr) wait_target = __ldcg(p.wait_target_dev);
+  if (p.wait_flags != nullptr && !wait_counters(p.wait_flags, p.wait_world, wait_target)) {
     // The activations never became ready.  Complete the armed stages with what is there
     // so that no copy is left in flight; the status word tells the caller.
     atomicExch(p.status, kStatusTimeout);
@@ -718,9 +733,9 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
             }
           });
         }
-        if (p.world > 0) __threadfence_system();  // this thread's stores into the other ranks' outputs
       }
-      // every warp of the team is done with the tile's partials before the ticket is reset
+      // every warp of the team is done with the tile's partials before the ticket is reset (and
+      // has issued its stores into the other ranks' outputs before the leader signals them)
       named_bar_sync(bar_id, FW * 32);
       if (leader) {
         if (prev == c_last - c_first) {
@@ -903,10 +918,8 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
     if (!whole) {
       mbar_arrive(bar_flush + 8 * ev);  // release: this thread's share of partial #ev is stored
       ++ev;
-    } else if (p.world > 0) {
-      __threadfence_system();  // this thread's stores into the other ranks' outputs
     }
-    named_bar_sync(1, nct);  // `red` is free again
+    named_bar_sync(1, nct);  // `red` is free again; a pushed tile's stores are issued
     if (whole && p.world > 0 && ctid == 0) signal_tile_delivered(p);
     if (trace && ctid == 0) trace[6] += 1;  // segments of this CTA
 
@@ -918,9 +931,25 @@ __global__ void __launch_bounds__(streamk_max_threads<OP, MT>(), 1)
 // Waits (bounded) until each of the `world` per-source arrival counters of this rank has
 // reached `target`, i.e. until every rank has delivered all its tiles of the calls enqueued so
 // far.  One thread; ordered on the stream, so whatever follows it sees the complete output.
+// Launched with programmatic stream serialization: the launch after it may start at once (a GEMM
+// then streams its first weight tiles while this kernel still waits; it touches nothing else before
+// its own griddepcontrol.wait, which returns when this kernel has completed), and this kernel itself
+// starts early and begins to look at the counters once everything before it in the stream is done.
 __global__ void fg_push_wait_kernel(const unsigned long long* flags, int world, unsigned long long target,
                                     int* status) {
+  griddep_launch_dependents();
+  griddep_wait();
   if (threadIdx.x != 0) return;
+  if (!wait_counters(flags, world, target)) atomicExch(status, kStatusTimeout);
+}
+// The same with the target read from device memory (the running total that pushing launches keep
+// in *target_dev): nothing in the launch changes from call to call, so it can be replayed in a graph.
+__global__ void fg_push_wait_dev_kernel(const unsigned long long* flags, int world,
+                                        const unsigned long long* target_dev, int* status) {
+  griddep_launch_dependents();
+  griddep_wait();  // the launches that add to *target_dev have completed
+  if (threadIdx.x != 0) return;
+  const unsigned long long target = __ldcg(target_dev);
   if (!wait_counters(flags, world, target)) atomicExch(status, kStatusTimeout);
 }
 

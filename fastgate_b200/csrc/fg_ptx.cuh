@@ -66,6 +66,9 @@ __device__ __forceinline__ void multimem_red_release_add_u64(unsigned long long*
 }
 // Release/acquire fence at GPU scope (__threadfence() is the sequentially consistent one).
 __device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
+// The same at system scope (other GPUs).  Cumulative: it also orders what other threads of the CTA
+// wrote before a barrier this thread has passed.
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ uint32_t smid() {
   uint32_t v;
   asm volatile("mov.u32 %0, %%smid;" : "=r"(v));

@@ -162,7 +162,7 @@ void op_wfirst_int4(at::Tensor W4, at::Tensor x, at::Tensor C, c10::optional<at:
 // and arrival counter (e.g. buffer_ptrs of a torch symmetric-memory allocation).
 void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std::vector<int64_t> flag_ptrs,
                     int64_t rank, int64_t n_total, int64_t wait_flag_ptr, int64_t wait_target, int64_t mc_c_ptr,
-                    int64_t mc_flag_ptr) {
+                    int64_t mc_flag_ptr, int64_t target_dev_ptr, int64_t wait_target_dev_ptr) {
   check_tensor(x, "activation", at::kHalf);
   check_tensor(W, "weight", at::kHalf);
   if (x.dim() != 2 || W.dim() != 2 || x.size(1) != W.size(1))
@@ -172,7 +172,7 @@ void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std
   const int64_t M = x.size(0), K = x.size(1), N = W.size(0);
   if (M == 0) return;
   if ((N % 128) != 0 || (K % 128) != 0) raise(FG_ERR_SHAPE, true);
-  fg_peers_t peers;
+  fg_peers_t peers = {};
   peers.world = static_cast<int>(c_ptrs.size());
   peers.rank = static_cast<int>(rank);
   peers.n_total = n_total;
@@ -180,6 +180,9 @@ void linear_nk_push(at::Tensor x, at::Tensor W, std::vector<int64_t> c_ptrs, std
   peers.wait_target = static_cast<unsigned long long>(wait_target);
   peers.mc_C = reinterpret_cast<void*>(mc_c_ptr);                       // multicast mappings, 0 = none
   peers.mc_flag = reinterpret_cast<unsigned long long*>(mc_flag_ptr);
+  // running totals kept on the device (0 = the caller counts): what makes the call replayable in a graph
+  peers.target_dev = reinterpret_cast<unsigned long long*>(target_dev_ptr);
+  peers.wait_target_dev = reinterpret_cast<const unsigned long long*>(wait_target_dev_ptr);
   for (size_t q = 0; q < c_ptrs.size(); ++q) {
     peers.C[q] = reinterpret_cast<void*>(c_ptrs[q]);
     peers.flag[q] = reinterpret_cast<unsigned long long*>(flag_ptrs[q]);
@@ -204,6 +207,17 @@ void push_wait(int64_t flag_ptr, int64_t world, int64_t target, int64_t device) 
   const int st = fg_push_wait(reinterpret_cast<const unsigned long long*>(flag_ptr), static_cast<int>(world),
                               static_cast<unsigned long long>(target), ws.buf.data_ptr(),
                               reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+}
+
+// The same wait with its target read on the device from the running total at target_dev_ptr.
+void push_wait_dev(int64_t flag_ptr, int64_t world, int64_t target_dev_ptr, int64_t device) {
+  const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(device).stream();
+  const Workspace ws = workspace_for(static_cast<int>(device), stream, 128);
+  const int st = fg_push_wait_dev(reinterpret_cast<const unsigned long long*>(flag_ptr), static_cast<int>(world),
+                                  reinterpret_cast<const unsigned long long*>(target_dev_ptr), ws.buf.data_ptr(),
+                                  reinterpret_cast<fg_stream_t>(stream));
   if (st != FG_OK) raise(st, true);
 }
 
@@ -402,8 +416,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("hgemm_tr", &hgemm_tr);
   m.def("linear_nk_push", &linear_nk_push, py::arg("x"), py::arg("W"), py::arg("c_ptrs"), py::arg("flag_ptrs"),
         py::arg("rank"), py::arg("n_total"), py::arg("wait_flag_ptr") = 0, py::arg("wait_target") = 0,
-        py::arg("mc_c_ptr") = 0, py::arg("mc_flag_ptr") = 0);
+        py::arg("mc_c_ptr") = 0, py::arg("mc_flag_ptr") = 0, py::arg("target_dev_ptr") = 0, py::arg("wait_target_dev_ptr") = 0);
   m.def("push_wait", &push_wait, py::arg("flag_ptr"), py::arg("world"), py::arg("target"), py::arg("device"));
+  m.def("push_wait_dev", &push_wait_dev, py::arg("flag_ptr"), py::arg("world"), py::arg("target_dev_ptr"), py::arg("device"));
   m.def("workspace_status", &workspace_status, py::arg("device"));
   m.def("prepack_kn_to_nk", &prepack_kn_to_nk, py::arg("B"), "B[K,N] fp16 -> W[N,K] fp16 (one-time repack for the NxK operators)");
   m.def("prepack_gate_up", &prepack_gate_up, py::arg("Wg"), py::arg("Wu"),

@@ -358,8 +358,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1)
       }
       if (whole) {
         if (p.world > 0) {
-          __threadfence_system();
-          named_bar_sync(1, 128);
+          named_bar_sync(1, 128);  // all four warps have issued the tile's stores
           if (threadIdx.x == 0) signal_tile_delivered(p);
         }
       } else {

@@ -45,6 +45,8 @@ struct GParams {
   int rank;
   unsigned long long* peer_flag[kMaxPeers];
   unsigned long long* mc_flag;  // multicast mapping of the flag arrays: tiles go out by multimem.st / multimem.red
+  unsigned long long* target_dev;  // optional: this rank's running total of tiles per source; a run adds total_tiles
+  uint32_t total_tiles;
 };
 
 // Position of one stage of the concatenated list.
@@ -118,6 +120,7 @@ __device__ __forceinline__ void group_signal(const GParams& g) {
     multimem_red_release_add_u64(g.mc_flag + g.rank, 1ull);
     return;
   }
+  fence_acq_rel_sys();  // one release for the stores of all threads that passed the barrier before this call
   for (int q = 0; q < g.world; ++q) atomicAdd_system(g.peer_flag[q] + g.rank, 1ull);
 }
 
@@ -238,6 +241,7 @@ __global__ void __launch_bounds__(kUmmaGroupThreads, 1) fg_umma_group_kernel(con
         cursor_advance(g, cw, 1);
       }
       griddep_wait();
+      if (blockIdx.x == 0 && g.target_dev != nullptr) atomicAdd(g.target_dev, static_cast<unsigned long long>(g.total_tiles));
       for (int i = 0; i < pre; ++i) {
         issue_x(i, cx, stage_chunks(cx));
         cursor_advance(g, cx, 1);
@@ -346,7 +350,6 @@ __global__ void __launch_bounds__(kUmmaGroupThreads, 1) fg_umma_group_kernel(con
               }
             }
           }
-          if (g.world > 0) __threadfence_system();
         }
         named_bar_sync(kFinBarrier, FW * 32);
         if (leader) {
@@ -470,7 +473,6 @@ __global__ void __launch_bounds__(kUmmaGroupThreads, 1) fg_umma_group_kernel(con
         for (int m = 0; m < MT; ++m)
           if (m < M) group_store1(g, c.e, m, n, __uint_as_float(r[m]));
         if (g.world > 0) {
-          __threadfence_system();
           named_bar_sync(1, 128);
           if (threadIdx.x == 0) group_signal(g);
         }

@@ -21,7 +21,7 @@ class LinearGroup:
     def __init__(self, xs: Sequence[torch.Tensor], Ws: Sequence[torch.Tensor], Cs: Optional[Sequence[torch.Tensor]],
                  weight_layout: str = "nk", peer_C_ptrs: Optional[Sequence[Sequence[int]]] = None,
                  flag_ptrs: Optional[Sequence[int]] = None, rank: int = 0, n_totals: Optional[Sequence[int]] = None,
-                 mc_C_ptrs: Optional[Sequence[int]] = None, mc_flag_ptr: int = 0):
+                 mc_C_ptrs: Optional[Sequence[int]] = None, mc_flag_ptr: int = 0, target_dev_ptr: int = 0):
         assert weight_layout in ("nk", "kn")
         n = len(xs)
         assert n == len(Ws) and n > 0
@@ -56,6 +56,9 @@ class LinearGroup:
                 peers.flag[r] = ptr
             if mc_flag_ptr and mc_C_ptrs is not None:
                 peers.mc_flag = mc_flag_ptr
+            # this rank's running total of tiles per source (device memory): every run adds self.tiles,
+            # so a run followed by push_wait_dev can be captured in a graph and replayed
+            peers.target_dev = target_dev_ptr or None
         L = capi.lib
         self._table = torch.empty(int(L.fg_group_table_bytes(n)), dtype=torch.uint8, device=self.device)
         handle = ctypes.c_void_p()

@@ -16,7 +16,9 @@ mappings (torch symmetric memory) and bumps each rank's arrival counter; a one-t
 kernel then holds the stream until all ranks' tiles have landed.  No NCCL call, no
 ``[g,M,N/g] -> [M,N]`` copy.  Peer stores and atomics over NVLink mappings, or, from 8 ranks on
 (``FASTGATE_MULTIMEM=0|1`` overrides), one ``multimem.st`` / ``multimem.red`` per tile that the
-NVSwitch replicates to every rank; never a TMA access to peer memory.
+NVSwitch replicates to every rank; never a TMA access to peer memory.  The number of tiles a rank
+expects is kept on the device next to the counters (pushing kernels add to it, waits read it), so a
+sequence of pushes and waits can be captured in a CUDA graph and replayed by every rank.
 
 A layer's push buffers are rewritten by every rank as soon as that rank's next call on the layer
 runs: call ``forward_push`` on a layer again only after every rank has consumed the previous
@@ -30,7 +32,6 @@ from typing import Callable, Optional
 import torch
 import torch.distributed as dist
 
-from . import capi
 from . import workloads as wl
 
 
@@ -85,7 +86,11 @@ class PushBuffers:
             self.c_ptrs = [self.out.data_ptr()]
             self.flag_ptrs = [self.flag.data_ptr()]
             self.mc_out = self.mc_flag = 0
-        self.target = 0  # tiles EACH rank will have delivered to this rank after the calls so far
+        # Tiles EACH rank will have delivered to this rank once the calls enqueued so far have run.
+        # The total lives on the device (word 8 of this rank's own flag array, which no other rank
+        # touches): pushing kernels add to it, waits read it, and nothing in a launch changes from
+        # call to call, so pushes and waits can be captured in a CUDA graph and replayed.
+        self.target_ptr = self.flag_ptrs[self.rank] + 8 * 8
 
 
 class ShardedLinear:
@@ -173,11 +178,11 @@ class ShardedLinear:
         pb = into if into is not None else self.push_buffers(max(M, 16), x.device, slot)
         if pb.n_total != self.n_total or pb.out.shape[0] < M:
             raise ValueError("fastgate_b200: push buffers do not fit this layer's output")
-        wait_ptr, wait_target = (after.flag_ptrs[after.rank], after.target) if after is not None else (0, 0)
-        ops.linear_nk_push(x, self.w, pb.c_ptrs, pb.flag_ptrs, pb.rank, self.n_total, wait_ptr, wait_target,
-                           pb.mc_out, pb.mc_flag)
-        # every pass over the weight delivers all of this rank's tiles once
-        pb.target += (self.w.shape[0] // 128) * capi.passes(capi.FG_OP_F16_NK, M, self.w.shape[0], self.w.shape[1])
+        wait_ptr, wait_target_ptr = (after.flag_ptrs[after.rank], after.target_ptr) if after is not None else (0, 0)
+        # every pass over the weight delivers all of this rank's tiles once and adds them to the
+        # buffers' running total on the device
+        ops.linear_nk_push(x, self.w, pb.c_ptrs, pb.flag_ptrs, pb.rank, self.n_total, wait_ptr, 0,
+                           pb.mc_out, pb.mc_flag, pb.target_ptr, wait_target_ptr)
         if wait:
             self.push_wait(pb)
         return pb.out[:M]
@@ -189,7 +194,7 @@ class ShardedLinear:
     def push_wait(self, pb: "PushBuffers") -> None:
         from . import ops
 
-        ops.push_wait(pb.flag_ptrs[pb.rank], pb.world, pb.target, pb.device.index if pb.device.index is not None else 0)
+        ops.push_wait_dev(pb.flag_ptrs[pb.rank], pb.world, pb.target_ptr, pb.device.index if pb.device.index is not None else 0)
 
 
 def shard_weight(weight: torch.Tensor, world: int, rank: int) -> torch.Tensor:

@@ -211,6 +211,18 @@ typedef struct fg_peers_t {
    * divides the NVLink egress of the push by world.  NULL = one store and one atomic per rank. */
   void* mc_C;
   unsigned long long* mc_flag;
+  /* Optional: the running totals kept in device memory instead of by the caller, so that a stream
+   * of pushes and waits can be captured in a CUDA graph and replayed (nothing in a launch then
+   * changes from call to call).  target_dev: one 64-bit word of this rank's device memory, zero at
+   * start, belonging to the output buffers this call pushes into; every launch of the call adds
+   * N_local/128 to it (so it always holds what every source rank will have delivered once the
+   * launches enqueued so far have run), for fg_push_wait_dev and for later calls that name it as
+   * wait_target_dev.  wait_target_dev: with wait_flags set, the kernel reads its wait target from
+   * this word (the target_dev of the layer that produced x) instead of wait_target, after the
+   * launches before it in the stream have completed.  NULL = the caller counts (wait_target,
+   * fg_push_wait). */
+  unsigned long long* target_dev;
+  const unsigned long long* wait_target_dev;
 } fg_peers_t;
 
 /* A layer's output buffers are written by every rank as soon as that rank's kernel runs: push
@@ -221,6 +233,10 @@ int fg_gemm_f16_nk_push(const void* x, const void* W_shard, int M, int N_local, 
                         const fg_peers_t* peers, void* ws, size_t ws_bytes, fg_stream_t stream);
 int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long long target, void* ws,
                  fg_stream_t stream);
+/* The same with the target read on the device from *target_dev (see fg_peers_t.target_dev) when the
+ * wait runs. */
+int fg_push_wait_dev(const unsigned long long* my_flags, int world, const unsigned long long* target_dev,
+                     void* ws, fg_stream_t stream);
 
 /* ---- grouped launch: many independent problems, one kernel ---------------------------
  * count problems C_i[M_i,N_i] = x_i[M_i,K_i] . W_i^T (fp16, M_i <= 16, the usual 128

@@ -89,6 +89,64 @@ def test_two_ranks_emulated_on_one_gpu(dev):
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
 
 
+def test_device_resident_targets_replay_in_a_graph(dev):
+    """With the running totals kept on the device nothing in a launch changes from call to call: two
+    chained layers and the closing wait are captured once and replayed; every replay adds the calls'
+    tiles to the totals and leaves the same bits."""
+    ws = gu.Workspace(dev)
+    M, K1, N1, N2 = 16, 512, 1024, 768
+    c1, c2 = wl.Case("gA", wl.OP_NK, M, N1, K1, 901), wl.Case("gB", wl.OP_NK, M, N2, N1, 902)
+    x, W1, W2 = wl.make_activation(c1).to(dev), wl.make_weight(c1).to(dev), wl.make_weight(c2).to(dev)
+    y1 = torch.zeros(M, N1, dtype=torch.float16, device=dev)
+    y2 = torch.zeros(M, N2, dtype=torch.float16, device=dev)
+    want1, want2 = torch.zeros_like(y1), torch.zeros_like(y2)
+    assert gu.call(wl.OP_NK, x, W1, None, want1, M, N1, K1, ws) == capi.FG_OK
+    assert gu.call(wl.OP_NK, want1, W2, None, want2, M, N2, N1, ws) == capi.FG_OK
+    f1 = torch.zeros(16, dtype=torch.int64, device=dev)  # counters [0, 8), the running total in word 8
+    f2 = torch.zeros(16, dtype=torch.int64, device=dev)
+    pa, pb = _peers(1, 0, N1, [y1], [f1]), _peers(1, 0, N2, [y2], [f2])
+    pa.target_dev = f1.data_ptr() + 64
+    pb.target_dev = f2.data_ptr() + 64
+    pb.wait_flags, pb.wait_target_dev = f1.data_ptr(), f1.data_ptr() + 64
+    L = capi.lib
+    side = torch.cuda.Stream()
+
+    def enqueue():
+        s = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        assert L.fg_gemm_f16_nk_push(x.data_ptr(), W1.data_ptr(), M, N1, K1, ctypes.byref(pa), ws.ptr, ws.bytes, s) == capi.FG_OK
+        assert L.fg_gemm_f16_nk_push(y1.data_ptr(), W2.data_ptr(), M, N2, N1, ctypes.byref(pb), ws.ptr, ws.bytes, s) == capi.FG_OK
+        assert L.fg_push_wait_dev(f2.data_ptr(), 1, f2.data_ptr() + 64, ws.ptr, s) == capi.FG_OK
+
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        enqueue()  # eager
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            enqueue()
+            enqueue()
+    runs = 1
+    for _ in range(3):
+        y1.fill_(float("nan"))
+        y2.fill_(float("nan"))
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        runs += 2
+        assert ws.status() == capi.FG_OK
+        assert f1[:9].tolist() == [runs * (N1 // 128)] + [0] * 7 + [runs * (N1 // 128)]
+        assert f2[:9].tolist() == [runs * (N2 // 128)] + [0] * 7 + [runs * (N2 // 128)]
+        assert torch.equal(y1.view(torch.int16), want1.view(torch.int16))
+        assert torch.equal(y2.view(torch.int16), want2.view(torch.int16))
+    # a wait on a total nobody will reach gives up and says so
+    f2[8] += 1
+    assert L.fg_push_wait_dev(f2.data_ptr(), 1, f2.data_ptr() + 64, ws.ptr, gu.stream()) == capi.FG_OK
+    torch.cuda.synchronize()
+    assert ws.status() == capi.FG_ERR_TIMEOUT
+    assert L.fg_push_wait_dev(f2.data_ptr(), 1, None, ws.ptr, gu.stream()) == capi.FG_ERR_NULL
+    assert L.fg_push_wait_dev(f2.data_ptr(), 1, f2.data_ptr() + 4, ws.ptr, gu.stream()) == capi.FG_ERR_ALIGN
+
+
 def test_wait_times_out_without_hanging(dev):
     """A counter nobody bumps: the wait kernel gives up after its budget and reports it in the
     workspace status word; the context stays usable."""
@@ -215,6 +273,26 @@ def _rank_main(rank, world, port, q, multimem):
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(y2.view(torch.int16), want2.view(torch.int16)))
             dist.barrier()  # nobody starts the next round while a slower rank still reads y1
+        # the same chain captured once per rank and replayed: the tile totals live on the device
+        xg = x1.to(dev)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            y1 = l1.forward_push(xg, wait=False, slot="graph")  # eager: allocates this slot's buffers on every rank
+            y2 = l2.forward_push(y1, wait=True, after=l1.last_push(16, "graph"), slot="graph")
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):  # NCCL's watchdog thread may call into CUDA meanwhile
+                y1 = l1.forward_push(xg, wait=False, slot="graph")
+                y2 = l2.forward_push(y1, wait=True, after=l1.last_push(16, "graph"), slot="graph")
+        for _ in range(3):
+            y2.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()  # every rank's copy is blank before anyone replays
+            graph.replay()
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(y2.view(torch.int16), want2.view(torch.int16)))
+            dist.barrier()
         # a grouped launch that pushes: three independent projections as one kernel per rank
         gcases = [wl.Case("g0", wl.OP_NK, 16, 1024, 512, 21), wl.Case("g1", wl.OP_NK, 5, 2048, 1024, 22), wl.Case("g2", wl.OP_NK, 16, 1024, 2304, 23)]
         gx = [wl.make_activation(c).to(dev) for c in gcases]
@@ -224,15 +302,15 @@ def _rank_main(rank, world, port, q, multimem):
         pbs = [lin.push_buffers(16, dev) for lin in glin]
         gflag = shard.PushBuffers(16, 128, dev)
         grp = LinearGroup(gx, [lin.w for lin in glin], None, peer_C_ptrs=[pb.c_ptrs for pb in pbs], flag_ptrs=gflag.flag_ptrs,
-                          rank=rank, n_totals=[c.N for c in gcases], mc_C_ptrs=[pb.mc_out for pb in pbs], mc_flag_ptr=gflag.mc_flag)
+                          rank=rank, n_totals=[c.N for c in gcases], mc_C_ptrs=[pb.mc_out for pb in pbs], mc_flag_ptr=gflag.mc_flag,
+                          target_dev_ptr=gflag.target_ptr)
         for _ in range(2):
             for pb in pbs:
                 pb.out.fill_(float("nan"))
             torch.cuda.synchronize()
             dist.barrier()
             grp.run()
-            gflag.target += grp.tiles
-            fg.push_wait(gflag.flag_ptrs[rank], world, gflag.target, rank)
+            fg.push_wait_dev(gflag.flag_ptrs[rank], world, gflag.target_ptr, rank)
             torch.cuda.synchronize()
             # the grouped kernel cuts the K sums at other places than the single calls behind `gwant`:
             # one fp16 rounding step apart from them, and bit-identical on every rank
