@@ -20,7 +20,7 @@ FG_OP_F16_KN, FG_OP_F16_NK, FG_OP_W8A16_NK, FG_OP_W4A16_NK = 0, 1, 2, 3
 EXPORTS = (
     "fg_plan", "fg_plan_validate", "fg_workspace_bytes", "fg_workspace_init", "fg_workspace_status",
     "fg_gemm_f16_kn", "fg_gemm_f16_nk", "fg_gemm_w8a16_nk", "fg_gemm_w4a16_nk", "fg_quantize_rows_w4", "fg_gemm_f16_nk_noalloc", "fg_noalloc_status", "fg_gemm_planned",
-    "fg_gemm_f16_nk_push", "fg_push_wait", "fg_push_wait_dev", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
+    "fg_gemm_f16_nk_push", "fg_push_wait", "fg_push_wait_dev", "fg_push_wait_dev_many", "fg_group_table_bytes", "fg_group_create", "fg_group_run",
     "fg_group_tiles", "fg_group_destroy", "fg_chain_table_bytes", "fg_chain_create", "fg_chain_workspace_bytes",
     "fg_chain_run", "fg_chain_grid", "fg_chain_trace_offset", "fg_chain_destroy", "fg_quantize_rows_w8", "fg_gemm_fused", "fg_linear_host",
     "fg_prepack_kn_to_nk", "fg_prepack_gate_up",
@@ -101,6 +101,7 @@ def _load() -> ctypes.CDLL:
     L.fg_gemm_f16_nk_push.argtypes = [vp, vp, i, i, i, ctypes.POINTER(Peers), vp, sz, vp]
     L.fg_push_wait.argtypes = [vp, i, ctypes.c_ulonglong, vp, vp]
     L.fg_push_wait_dev.argtypes = [vp, i, vp, vp, vp]
+    L.fg_push_wait_dev_many.argtypes = [vp, vp, i, i, vp, vp]
     L.fg_group_table_bytes.argtypes = [i]
     L.fg_group_table_bytes.restype = sz
     L.fg_group_create.argtypes = [i, ctypes.POINTER(Problem), i, ctypes.POINTER(Peers), vp, sz, ctypes.POINTER(vp)]

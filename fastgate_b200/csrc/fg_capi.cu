@@ -627,6 +627,29 @@ int fg_push_wait_dev(const unsigned long long* my_flags, int world, const unsign
   return FG_OK;
 }
 
+int fg_push_wait_dev_many(const unsigned long long* const* my_flags, const unsigned long long* const* target_dev, int count,
+                          int world, void* ws, fg_stream_t stream) {
+  if (my_flags == nullptr || target_dev == nullptr || ws == nullptr) return FG_ERR_NULL;
+  if (world < 1 || world > fg::kMaxPeers || count < 1 || count > fg::kMaxWaits) return FG_ERR_PLAN;
+  fg::WaitList w = {};
+  w.count = count;
+  for (int i = 0; i < count; ++i) {
+    if (my_flags[i] == nullptr || target_dev[i] == nullptr) return FG_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(my_flags[i]) & 7u) != 0 || (reinterpret_cast<uintptr_t>(target_dev[i]) & 7u) != 0)
+      return FG_ERR_ALIGN;
+    w.flags[i] = my_flags[i];
+    w.target_dev[i] = target_dev[i];
+  }
+  const cudaError_t e = launch_wait(fg::fg_push_wait_many_kernel, reinterpret_cast<cudaStream_t>(stream), w, world,
+                                    static_cast<int*>(ws));
+  if (e != cudaSuccess) {
+    g_last_cuda = static_cast<int>(e);
+    return FG_ERR_CUDA;
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FG_OK;
+}
+
 // ---- grouped launch ------------------------------------------------------------------
 struct fg_group {
   int op;

@@ -953,4 +953,20 @@ __global__ void fg_push_wait_dev_kernel(const unsigned long long* flags, int wor
   if (!wait_counters(flags, world, target)) atomicExch(status, kStatusTimeout);
 }
 
+// Several such waits in one launch (one lane per flag array): the step of a caller that closes
+// many pushed outputs at once pays one launch instead of one per output.
+constexpr int kMaxWaits = 16;
+struct WaitList {
+  const unsigned long long* flags[kMaxWaits];
+  const unsigned long long* target_dev[kMaxWaits];
+  int count;
+};
+__global__ void fg_push_wait_many_kernel(const WaitList w, int world, int* status) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int i = threadIdx.x;
+  if (i >= w.count) return;
+  if (!wait_counters(w.flags[i], world, __ldcg(w.target_dev[i]))) atomicExch(status, kStatusTimeout);
+}
+
 }  // namespace fg

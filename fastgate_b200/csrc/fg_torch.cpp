@@ -221,6 +221,22 @@ void push_wait_dev(int64_t flag_ptr, int64_t world, int64_t target_dev_ptr, int6
   if (st != FG_OK) raise(st, true);
 }
 
+// Several such waits as one launch.
+void push_wait_dev_many(std::vector<int64_t> flag_ptrs, std::vector<int64_t> target_dev_ptrs, int64_t world, int64_t device) {
+  if (flag_ptrs.size() != target_dev_ptrs.size() || flag_ptrs.empty()) throw std::runtime_error("fastgate_b200: one total per flag array expected");
+  const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
+  cudaStream_t stream = at::cuda::getCurrentCUDAStream(device).stream();
+  const Workspace ws = workspace_for(static_cast<int>(device), stream, 128);
+  std::vector<const unsigned long long*> f, t;
+  for (size_t i = 0; i < flag_ptrs.size(); ++i) {
+    f.push_back(reinterpret_cast<const unsigned long long*>(flag_ptrs[i]));
+    t.push_back(reinterpret_cast<const unsigned long long*>(target_dev_ptrs[i]));
+  }
+  const int st = fg_push_wait_dev_many(f.data(), t.data(), static_cast<int>(f.size()), static_cast<int>(world), ws.buf.data_ptr(),
+                                       reinterpret_cast<fg_stream_t>(stream));
+  if (st != FG_OK) raise(st, true);
+}
+
 // Device status word of the current stream's workspace (synchronises the stream).
 int64_t workspace_status(int64_t device) {
   const c10::cuda::CUDAGuard guard(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
@@ -419,6 +435,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("mc_c_ptr") = 0, py::arg("mc_flag_ptr") = 0, py::arg("target_dev_ptr") = 0, py::arg("wait_target_dev_ptr") = 0);
   m.def("push_wait", &push_wait, py::arg("flag_ptr"), py::arg("world"), py::arg("target"), py::arg("device"));
   m.def("push_wait_dev", &push_wait_dev, py::arg("flag_ptr"), py::arg("world"), py::arg("target_dev_ptr"), py::arg("device"));
+  m.def("push_wait_dev_many", &push_wait_dev_many, py::arg("flag_ptrs"), py::arg("target_dev_ptrs"), py::arg("world"), py::arg("device"));
   m.def("workspace_status", &workspace_status, py::arg("device"));
   m.def("prepack_kn_to_nk", &prepack_kn_to_nk, py::arg("B"), "B[K,N] fp16 -> W[N,K] fp16 (one-time repack for the NxK operators)");
   m.def("prepack_gate_up", &prepack_gate_up, py::arg("Wg"), py::arg("Wu"),

@@ -33,7 +33,7 @@ BZ_OPS = (
 )
 COMPARATORS = ("hgemm", "hgemm_tr")
 
-EXTRA = ("linear_nk_push", "push_wait", "push_wait_dev", "workspace_status", "quantize_int8", "linear_fused", "fastgemv_int4",
+EXTRA = ("linear_nk_push", "push_wait", "push_wait_dev", "push_wait_dev_many", "workspace_status", "quantize_int8", "linear_fused", "fastgemv_int4",
          "quantize_int4", "prepack_kn_to_nk", "prepack_gate_up")
 
 __all__ = list(KN_OPS + NK_OPS + WF_OPS + COMPARATORS + EXTRA) + ["launch_count", "version",

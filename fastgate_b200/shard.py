@@ -197,6 +197,18 @@ class ShardedLinear:
         ops.push_wait_dev(pb.flag_ptrs[pb.rank], pb.world, pb.target_ptr, pb.device.index if pb.device.index is not None else 0)
 
 
+def push_wait_all(pbs) -> None:
+    """One wait kernel for several pushed outputs (up to 16 per launch): the current stream holds until
+    every rank's tiles of all of them have landed here."""
+    from . import ops
+
+    pbs = list(pbs)
+    for i in range(0, len(pbs), 16):
+        part = pbs[i:i + 16]
+        dev = part[0].device.index if part[0].device.index is not None else 0
+        ops.push_wait_dev_many([pb.flag_ptrs[pb.rank] for pb in part], [pb.target_ptr for pb in part], part[0].world, dev)
+
+
 def shard_weight(weight: torch.Tensor, world: int, rank: int) -> torch.Tensor:
     """Rows [r*N/g, (r+1)*N/g) of an NxK weight (a view; call .contiguous() before upload)."""
     b, e = wl.shard_rows(weight.shape[0], world, rank)

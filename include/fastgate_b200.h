@@ -237,6 +237,9 @@ int fg_push_wait(const unsigned long long* my_flags, int world, unsigned long lo
  * wait runs. */
 int fg_push_wait_dev(const unsigned long long* my_flags, int world, const unsigned long long* target_dev,
                      void* ws, fg_stream_t stream);
+/* count (1..16) such waits as one launch: my_flags[i] / target_dev[i] are host arrays of device pointers. */
+int fg_push_wait_dev_many(const unsigned long long* const* my_flags, const unsigned long long* const* target_dev,
+                          int count, int world, void* ws, fg_stream_t stream);
 
 /* ---- grouped launch: many independent problems, one kernel ---------------------------
  * count problems C_i[M_i,N_i] = x_i[M_i,K_i] . W_i^T (fp16, M_i <= 16, the usual 128

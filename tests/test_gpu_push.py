@@ -138,8 +138,18 @@ def test_device_resident_targets_replay_in_a_graph(dev):
         assert f2[:9].tolist() == [runs * (N2 // 128)] + [0] * 7 + [runs * (N2 // 128)]
         assert torch.equal(y1.view(torch.int16), want1.view(torch.int16))
         assert torch.equal(y2.view(torch.int16), want2.view(torch.int16))
+    # both outputs closed by one wait kernel
+    fl = (ctypes.c_void_p * 2)(f1.data_ptr(), f2.data_ptr())
+    tg = (ctypes.c_void_p * 2)(f1.data_ptr() + 64, f2.data_ptr() + 64)
+    assert L.fg_push_wait_dev_many(fl, tg, 2, 1, ws.ptr, gu.stream()) == capi.FG_OK
+    torch.cuda.synchronize()
+    assert ws.status() == capi.FG_OK
+    assert L.fg_push_wait_dev_many(fl, tg, 17, 1, ws.ptr, gu.stream()) == capi.FG_ERR_PLAN
     # a wait on a total nobody will reach gives up and says so
     f2[8] += 1
+    assert L.fg_push_wait_dev_many(fl, tg, 2, 1, ws.ptr, gu.stream()) == capi.FG_OK
+    torch.cuda.synchronize()
+    assert ws.status() == capi.FG_ERR_TIMEOUT
     assert L.fg_push_wait_dev(f2.data_ptr(), 1, f2.data_ptr() + 64, ws.ptr, gu.stream()) == capi.FG_OK
     torch.cuda.synchronize()
     assert ws.status() == capi.FG_ERR_TIMEOUT
@@ -273,6 +283,15 @@ def _rank_main(rank, world, port, q, multimem):
             torch.cuda.synchronize()
             ok = ok and bool(torch.equal(y2.view(torch.int16), want2.view(torch.int16)))
             dist.barrier()  # nobody starts the next round while a slower rank still reads y1
+        # two independent pushes closed by one wait kernel
+        for _ in range(2):
+            ya = l1.forward_push(x1.to(dev), wait=False, slot="a")
+            yb = l2.forward_push(want2, wait=False, slot="b")
+            shard.push_wait_all([l1.last_push(16, "a"), l2.last_push(16, "b")])
+            torch.cuda.synchronize()
+            ok = ok and bool(torch.equal(ya.view(torch.int16), l1.forward(x1.to(dev)).view(torch.int16)))
+            ok = ok and bool(torch.equal(yb.view(torch.int16), l2.forward(want2).view(torch.int16)))
+            dist.barrier()
         # the same chain captured once per rank and replayed: the tile totals live on the device
         xg = x1.to(dev)
         side = torch.cuda.Stream()
