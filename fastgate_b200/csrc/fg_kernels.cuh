@@ -415,9 +415,9 @@ __device__ __forceinline__ float epilogue1(const KParams& p, int m, int n, float
   return v;
 }
 
-// Scale (int8 op), fused epilogue, round and store two adjacent outputs of row m.
+// Scale (int8 op), fused epilogue and rounding of two adjacent outputs of row m.
 template <int OP, int ACT>
-__device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float2 v) {
+__device__ __forceinline__ __half2 finish_out2(const KParams& p, int m, int n, float2 v) {
   if ((OP == kOpW8A16NK || (OP == kOpW4A16NK && p.scale_groups <= 1)) && p.scales != nullptr) {
     const float2 sc = __half22float2(*reinterpret_cast<const __half2*>(p.scales + n));
     v.x *= sc.x;
@@ -427,7 +427,13 @@ __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float
     v.x = epilogue1<ACT>(p, m, n, v.x);
     v.y = epilogue1<ACT>(p, m, n + 1, v.y);
   }
-  const __half2 h = __floats2half2_rn(v.x, v.y);
+  return __floats2half2_rn(v.x, v.y);
+}
+
+// ... and their store (local, multicast or one store per rank).
+template <int OP, int ACT>
+__device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float2 v) {
+  const __half2 h = finish_out2<OP, ACT>(p, m, n, v);
   if (p.world == 0) {
     *reinterpret_cast<__half2*>(out_ptr(p, m, n)) = h;
   } else if (p.mc_C != nullptr) {
@@ -436,6 +442,25 @@ __device__ __forceinline__ void store_out2(const KParams& p, int m, int n, float
     const size_t off = static_cast<size_t>(m) * p.ldc + p.col0 + n;
     for (int q = 0; q < p.world; ++q) *reinterpret_cast<__half2*>(p.peer_C[q] + off) = h;
   }
+}
+
+// Four adjacent outputs (n a multiple of 4).  A pushed tile goes out in 8-byte pieces: a warp of the
+// finishing team then writes whole 256-byte runs of a row per instruction, which is what the NVLink
+// packets of a peer store are made from.
+template <int OP, int ACT>
+__device__ __forceinline__ void store_out4(const KParams& p, int m, int n, float4 v) {
+  if (p.world == 0 || p.mc_C != nullptr) {
+    store_out2<OP, ACT>(p, m, n, make_float2(v.x, v.y));
+    store_out2<OP, ACT>(p, m, n + 2, make_float2(v.z, v.w));
+    return;
+  }
+  const __half2 lo = finish_out2<OP, ACT>(p, m, n, make_float2(v.x, v.y));
+  const __half2 hi = finish_out2<OP, ACT>(p, m, n + 2, make_float2(v.z, v.w));
+  uint2 w;
+  w.x = *reinterpret_cast<const uint32_t*>(&lo);
+  w.y = *reinterpret_cast<const uint32_t*>(&hi);
+  const size_t off = static_cast<size_t>(m) * p.ldc + p.col0 + n;
+  for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint2*>(p.peer_C[q] + off) = w;
 }
 
 // One thread tells every rank that one more output tile of this rank has been delivered.
@@ -726,10 +751,7 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int m = m0 + i;
-              if (m < p.M) {
-                store_out2<OP, ACT>(p, m, n0, make_float2(sum[i].x, sum[i].y));
-                store_out2<OP, ACT>(p, m, n0 + 2, make_float2(sum[i].z, sum[i].w));
-              }
+              if (m < p.M) store_out4<OP, ACT>(p, m, n0, sum[i]);
             }
           });
         }
