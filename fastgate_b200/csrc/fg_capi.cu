@@ -264,7 +264,7 @@ int run_gemv(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
     }
   }
   uint8_t* wsb = static_cast<uint8_t*>(ws);
-  fg::GemvParams p;
+  fg::GemvParams p = {};
   p.W = W;
   p.x = static_cast<const __half*>(x);
   p.C = static_cast<__half*>(C);
@@ -347,7 +347,7 @@ int run_planned(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void*
   if (st != FG_OK) return st;
 
   uint8_t* wsb = static_cast<uint8_t*>(ws);
-  fg::KParams p;
+  fg::KParams p = {};
   p.scales = static_cast<const __half*>(scales);
   p.scale_groups = qa ? qa->groups : 1;
   {
@@ -809,7 +809,7 @@ int fg_group_run(const fg_group_t* grp, void* ws, size_t ws_bytes, fg_stream_t s
   }
   lk.unlock();
   uint8_t* wsb = static_cast<uint8_t*>(ws);
-  fg::GParams g;
+  fg::GParams g = {};
   g.table = grp->table_dev;
   g.count = grp->count;
   g.total_units = grp->total_units;
@@ -1004,7 +1004,7 @@ int fg_chain_run(const fg_chain_t* ch, void* ws, size_t ws_bytes, fg_stream_t st
     g_last_cuda = static_cast<int>(e);
     return FG_ERR_CUDA;
   }
-  fg::CParams g;
+  fg::CParams g = {};
   g.table = ch->table_dev;
   g.count = ch->count;
   g.partials = reinterpret_cast<float*>(wsb + FG_WS_HEADER_BYTES);
@@ -1227,7 +1227,7 @@ int fg_gemm_f16_nk_noalloc(const void* x, const void* W, void* C, int M, int N, 
   CUtensorMap tmW;
   if ((st = encode_2d(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, W, K, N, 64, 128)) != FG_OK) return st;
 
-  fg::KParams p;
+  fg::KParams p = {};
   p.scales = nullptr;
   p.status = reinterpret_cast<int*>(scratch);
   p.tickets = reinterpret_cast<unsigned int*>(scratch + kNoAllocTicketsOffset);
