@@ -74,7 +74,7 @@ struct DeviceInfo {
   int cc_major = 0;
   int smem_set[4][2] = {{0, 0}, {0, 0}, {0, 0}, {0, 0}};  // largest dynamic smem opted in per kernel
   int smem_set_umma[4][3] = {};
-  int smem_set_gemv[FG_GEMV_MAX_M] = {};
+  int smem_set_gemv[FG_GEMV_MAX_M + 1] = {};  // fp16 with one and two rows, int8
   int smem_set_group[2] = {0, 0};
   int smem_set_chain[2] = {0, 0};
 };
@@ -243,16 +243,20 @@ int launch_one(const fg_plan_t& pl, KernelFn kern, const CUtensorMap& tmW, const
 // ---- row-split GEMV kernel (plan.math == 4) -------------------------------------------------
 using GemvFn = void (*)(const fg::GemvParams);
 
-GemvFn pick_gemv_kernel(int M) { return M == 1 ? fg::fg_gemv_kernel<1> : fg::fg_gemv_kernel<2>; }
+GemvFn pick_gemv_kernel(int M, bool int8) {
+  if (int8) return fg::fg_gemv_kernel<1, 1>;
+  return M == 1 ? fg::fg_gemv_kernel<1> : fg::fg_gemv_kernel<2>;
+}
 
 int run_gemv(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W, const void* scales, void* C, int M,
              int N, int K, void* ws, cudaStream_t stream, const fg_epilogue_t* ep) {
   if (M != pl.m_tile || M < 1 || M > FG_GEMV_MAX_M) return FG_ERR_PLAN;
-  if (pl.op != FG_OP_F16_NK) return FG_ERR_PLAN;
-  GemvFn kern = pick_gemv_kernel(M);
+  const bool int8 = (pl.op == FG_OP_W8A16_NK);
+  if (pl.op != FG_OP_F16_NK && !(int8 && M == 1)) return FG_ERR_PLAN;
+  GemvFn kern = pick_gemv_kernel(M, int8);
   {
     std::lock_guard<std::mutex> lk(g_dev_mu);
-    int& set = dev->smem_set_gemv[M - 1];
+    int& set = dev->smem_set_gemv[int8 ? 2 : M - 1];
     if (pl.smem_bytes > set) {
       const cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kern),
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, pl.smem_bytes);
@@ -268,7 +272,7 @@ int run_gemv(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
   p.W = W;
   p.x = static_cast<const __half*>(x);
   p.C = static_cast<__half*>(C);
-  (void)scales;
+  p.scales = int8 ? static_cast<const __half*>(scales) : nullptr;
   p.bias = ep ? static_cast<const __half*>(ep->bias) : nullptr;
   p.residual = ep ? static_cast<const __half*>(ep->residual) : nullptr;
   p.act = ep ? ep->act : 0;
@@ -280,7 +284,7 @@ int run_gemv(const fg_plan_t& pl, DeviceInfo* dev, const void* x, const void* W,
   p.N = N;
   p.K = K;
   p.rows_per_stage = pl.rows_per_stage;
-  p.stage_bytes = pl.rows_per_stage * K * 2;
+  p.stage_bytes = pl.rows_per_stage * K * (int8 ? 1 : 2);
   p.stages = pl.stages;
   p.static_rows = pl.static_rows;
   p.l2_prefetch_bytes = pl.pdl ? FG_GEMV_L2_PREFETCH_BYTES : 0;

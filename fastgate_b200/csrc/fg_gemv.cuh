@@ -41,7 +41,8 @@ constexpr int kGemvMaxM = 2;
 constexpr int kGemvMaxOut = 8;      // rows per stage x token rows: outputs one stage produces
 
 struct GemvParams {
-  const void* W;             // [N, K] fp16
+  const void* W;             // [N, K] fp16, or int8 (then M == 1)
+  const __half* scales;      // int8 weights: one fp16 scale per row, or nullptr (scale 1)
   const __half* x;           // [M, K]
   __half* C;                 // [M, N]
   const __half* bias;        // [N] or nullptr
@@ -84,6 +85,51 @@ __device__ __forceinline__ void fma_f16x2_f32(float& acc0, float& acc1, uint32_t
       : "r"(w), "r"(x));
 }
 
+// Four int8 weights (one 32-bit word, k ascending with the byte index) against four fp16 activations
+// (two words).  An int8 b becomes the fp16 number b exactly in three integer-pipe steps: flip the sign
+// bit (b + 128 as an unsigned byte), put the byte under the exponent of 1024 (0x6400 | byte = 1024 +
+// byte, two bytes per `prmt`), subtract 1152.
+__device__ __forceinline__ void fma_i8x4_f32(float& acc0, float& acc1, uint32_t w, uint32_t x01, uint32_t x23) {
+  const uint32_t u = w ^ 0x80808080u;
+  uint32_t h01, h23;
+  asm("prmt.b32 %0, %1, %2, 0x4140;" : "=r"(h01) : "r"(u), "r"(0x64646464u));
+  asm("prmt.b32 %0, %1, %2, 0x4342;" : "=r"(h23) : "r"(u), "r"(0x64646464u));
+  asm("sub.rn.f16x2 %0, %0, %1;" : "+r"(h01) : "r"(0x64806480u));
+  asm("sub.rn.f16x2 %0, %0, %1;" : "+r"(h23) : "r"(0x64806480u));
+  fma_f16x2_f32(acc0, acc1, h01, x01);
+  fma_f16x2_f32(acc0, acc1, h23, x23);
+}
+
+// The same stage for int8 weights (one token row): lane l takes the 16-byte pieces l, l + 32, ... of
+// every row, sixteen k each, against 32 bytes of x.
+template <int RB>
+__device__ __forceinline__ void gemv_stage_i8(uint32_t wbase, uint32_t xbase, int K, int nrows, int lane,
+                                              float (&out)[kGemvMaxOut]) {
+  const int pieces = K >> 4;
+  const uint32_t row_bytes = static_cast<uint32_t>(K);
+  float acc[RB][4];
+#pragma unroll
+  for (int r = 0; r < RB; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+#pragma unroll 4
+  for (int i = lane; i < pieces; i += 32) {
+    uint32_t xv[8];
+    lds_v4(xbase + i * 32, xv[0], xv[1], xv[2], xv[3]);
+    lds_v4(xbase + i * 32 + 16, xv[4], xv[5], xv[6], xv[7]);
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      if (RB > 1 && r >= nrows) break;
+      uint32_t wv[4];
+      lds_v4(wbase + r * row_bytes + i * 16, wv[0], wv[1], wv[2], wv[3]);
+      fma_i8x4_f32(acc[r][0], acc[r][1], wv[0], xv[0], xv[1]);
+      fma_i8x4_f32(acc[r][2], acc[r][3], wv[1], xv[2], xv[3]);
+      fma_i8x4_f32(acc[r][0], acc[r][1], wv[2], xv[4], xv[5]);
+      fma_i8x4_f32(acc[r][2], acc[r][3], wv[3], xv[6], xv[7]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RB; ++r) out[r] = (acc[r][0] + acc[r][1]) + (acc[r][2] + acc[r][3]);
+}
+
 // One stage, one warp: RB rows (nrows of them valid) against the M rows of x in shared memory.
 // Lane l takes the 16-byte pieces l, l + 32, ... of every row; even and odd k go to separate
 // accumulators so that two FMA chains are in flight per output.
@@ -119,10 +165,12 @@ __device__ __forceinline__ void gemv_stage(uint32_t wbase, uint32_t xbase, int K
     for (int m = 0; m < M; ++m) out[r * M + m] = acc[r][m][0] + acc[r][m][1];
 }
 
-template <int M>
+// WB = bytes per weight: 2 (fp16) or 1 (int8, one token row, per-row scale in the epilogue).
+template <int M, int WB = 2>
 __global__ void __launch_bounds__((kGemvMaxWarps + 1) * 32, 1) fg_gemv_kernel(const GemvParams p) {
   static_assert(M >= 1 && M <= kGemvMaxM, "token rows");
-  constexpr int wbytes = 2;
+  static_assert(WB == 2 || (WB == 1 && M == 1), "int8 weights: one token row");
+  constexpr int wbytes = WB;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 127u) & ~127u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -296,11 +344,20 @@ __global__ void __launch_bounds__((kGemvMaxWarps + 1) * 32, 1) fg_gemv_kernel(co
 #pragma unroll
       for (int i = 0; i < kGemvMaxOut; ++i) out[i] = 0.f;
       const uint32_t wbase = ring_base + s * p.stage_bytes;
-      switch (RB) {
-        case 1: gemv_stage<M, 1>(wbase, smem_base, K, nrows, lane, out); break;
-        case 2: if constexpr (2 * M <= kGemvMaxOut) gemv_stage<M, 2>(wbase, smem_base, K, nrows, lane, out); break;
-        case 4: if constexpr (4 * M <= kGemvMaxOut) gemv_stage<M, 4>(wbase, smem_base, K, nrows, lane, out); break;
-        default: if constexpr (8 * M <= kGemvMaxOut) gemv_stage<M, 8>(wbase, smem_base, K, nrows, lane, out); break;
+      if constexpr (WB == 1) {
+        switch (RB) {
+          case 1: gemv_stage_i8<1>(wbase, smem_base, K, nrows, lane, out); break;
+          case 2: gemv_stage_i8<2>(wbase, smem_base, K, nrows, lane, out); break;
+          case 4: gemv_stage_i8<4>(wbase, smem_base, K, nrows, lane, out); break;
+          default: gemv_stage_i8<8>(wbase, smem_base, K, nrows, lane, out); break;
+        }
+      } else {
+        switch (RB) {
+          case 1: gemv_stage<M, 1>(wbase, smem_base, K, nrows, lane, out); break;
+          case 2: if constexpr (2 * M <= kGemvMaxOut) gemv_stage<M, 2>(wbase, smem_base, K, nrows, lane, out); break;
+          case 4: if constexpr (4 * M <= kGemvMaxOut) gemv_stage<M, 4>(wbase, smem_base, K, nrows, lane, out); break;
+          default: if constexpr (8 * M <= kGemvMaxOut) gemv_stage<M, 8>(wbase, smem_base, K, nrows, lane, out); break;
+        }
       }
       // the stage's bytes have been read: hand the slot back before the sums are finished
       __syncwarp();
@@ -320,6 +377,7 @@ __global__ void __launch_bounds__((kGemvMaxWarps + 1) * 32, 1) fg_gemv_kernel(co
         const int m = lane / nrows, r = lane - m * nrows;
         const int n = row0 + r;
         float v = mine;
+        if (WB == 1 && p.scales != nullptr) v *= __half2float(p.scales[n]);  // one scale per output channel, in fp32
         if (p.bias != nullptr) v += __half2float(p.bias[n]);
         switch (p.act) {
           case kActGeluErf: v = act_fn<kActGeluErf>(v); break;

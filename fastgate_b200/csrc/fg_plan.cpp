@@ -48,6 +48,8 @@ static int gemv_max_m() {
 }
 
 static bool gemv_eligible(int op, int M, int K) {
+  if (op == FG_OP_W8A16_NK)  // int8 rows: one token row (the conversion triples the instructions per byte)
+    return M == 1 && gemv_max_m() >= 1 && K >= 2 * FG_GEMV_MIN_K && K * 2 <= 65536 && (K % 16) == 0;
   return op == FG_OP_F16_NK && M <= gemv_max_m() && K >= FG_GEMV_MIN_K && static_cast<long long>(M) * K * 2 <= 65536 &&
          K * 2 <= FG_GEMV_MAX_STAGE_BYTES;
 }
@@ -61,7 +63,7 @@ static int plan_gemv(int op, int M, int N, int K, int sm_count, int smem_optin_b
   p.passes = 1;
   p.tiles = N / 128;
   p.pdl = 1;
-  const int row_bytes = K * 2;
+  const int row_bytes = K * (op == FG_OP_W8A16_NK ? 1 : 2);
   int rows = FG_GEMV_MAX_OUT;
   while (rows > 1 && (rows * row_bytes > FG_GEMV_STAGE_TARGET_BYTES || rows * M > FG_GEMV_MAX_OUT)) rows >>= 1;
   p.rows_per_stage = rows;

@@ -174,9 +174,9 @@ def test_fused_epilogue(act, M, dev, ws):
 
 
 def test_the_tiled_kernels_take_what_the_gemv_kernel_cannot(dev, ws):
-    """Three rows and more, rows too short or too long for a ring of whole rows, KxN weights: other plans."""
+    """Three rows and more, rows too short or too long for a ring of whole rows, KxN weights, int8 weights with two rows: other plans."""
     for (op, M, N, K) in [(wl.OP_NK, 3, 4096, 4096), (wl.OP_NK, 1, 256, 512), (wl.OP_NK, 1, 256, 32768), (wl.OP_KN, 1, 4096, 4096),
-                          (wl.OP_W8, 1, 4096, 4096)]:
+                          (wl.OP_W8, 2, 4096, 4096)]:
         assert capi.plan(op, M, N, K, 148, 232448).math != 4
     for (M, N, K) in [(1, 256, 512), (2, 128, 32768)]:
         case = wl.Case("not_gemv", wl.OP_NK, M, N, K, 7400 + M)
@@ -184,3 +184,78 @@ def test_the_tiled_kernels_take_what_the_gemv_kernel_cannot(dev, ws):
         out = torch.zeros(M, N, dtype=torch.float16, device=dev)
         assert gu.call(wl.OP_NK, x.to(dev), W.to(dev), None, out, M, N, K, ws) == capi.FG_OK
         oracle.check_tolerance(out.cpu().numpy(), oracle.gemm_nk(x.numpy(), W.numpy()), case.name)
+
+
+# ---- int8 weights, one token row --------------------------------------------------------------
+W8_SHAPES = [(28672, 8192), (4096, 4096), (128, 2048), (11008, 4096), (384, 16384), (1152, 2304), (256, 32768)]
+
+
+def _w8_case(N, K, seed):
+    case = wl.Case(f"gemv_w8_N{N}_K{K}", wl.OP_W8, 1, N, K, seed)
+    return case, wl.make_activation(case), wl.make_weight(case), wl.make_scales(case)
+
+
+@pytest.mark.parametrize("N,K", W8_SHAPES)
+@pytest.mark.parametrize("scaled", [True, False])
+def test_int8_gemv_matches_the_oracle(N, K, scaled, dev, ws):
+    """fastgemv_int8's shape class on the row-split kernel: exact int8 -> fp16 conversion, fp32 sums, one
+    scale per output channel in the epilogue.  Twice, bit for bit; against the tiled kernel within the tolerance."""
+    case, x, W, sc = _w8_case(N, K, 7500 + N + K)
+    sc = sc if scaled else None
+    p = capi.plan(wl.OP_W8, 1, N, K, 148, 232448)
+    assert p.math == 4 and p.m_tile == 1 and p.rows_per_stage * K <= 65536, p.as_dict()
+    ref = oracle.gemm_w8a16_nk(x.numpy(), W.numpy(), sc.numpy() if scaled else None)
+    xd, Wd = x.to(dev), W.to(dev)
+    sd = sc.to(dev) if scaled else None
+    outs = []
+    for _ in range(2):
+        g = gu.GuardedOut(1, N, dev)
+        st = gu.call(wl.OP_W8, xd, Wd, sd, g.out, 1, N, K, ws)
+        assert st == capi.FG_OK, capi.status_str(st)
+        torch.cuda.synchronize()
+        assert ws.status() == capi.FG_OK and counters(ws) == (0, 0)
+        g.check_canaries()
+        outs.append(g.out)
+    oracle.check_tolerance(gu.to_np(outs[0]), ref, case.name)
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    tiled = capi.Plan()
+    assert L.fg_plan_mma_sync(wl.OP_W8, 1, N, K, 148, 232448, ctypes.byref(tiled)) == capi.FG_OK and tiled.math == 0
+    t = gu.GuardedOut(1, N, dev)
+    assert gu.call(wl.OP_W8, xd, Wd, sd, t.out, 1, N, K, ws, tiled) == capi.FG_OK
+    torch.cuda.synchronize()
+    oracle.check_tolerance(gu.to_np(t.out), ref, case.name + " tiled")
+
+
+def test_int8_gemv_extreme_weights_and_one_hot(dev, ws):
+    """Every int8 value converts exactly: a one-hot activation reads single weights back, scaled by one."""
+    N, K = 256, 2048
+    W = (torch.arange(N * K, dtype=torch.int64).reshape(N, K) * 37 % 255 - 127).to(torch.int8)
+    W[0, :256] = torch.arange(-128, 128, dtype=torch.int64).to(torch.int8)[:256]
+    Wd = W.to(dev)
+    for k in (0, 1, 2, 3, 15, 16, 255, 1024, 2047):
+        x = torch.zeros(1, K, dtype=torch.float16)
+        x[0, k] = 1
+        out = torch.zeros(1, N, dtype=torch.float16, device=dev)
+        assert gu.call(wl.OP_W8, x.to(dev), Wd, None, out, 1, N, K, ws) == capi.FG_OK
+        assert torch.equal(out.cpu()[0], W[:, k].to(torch.float16)), k
+
+
+def test_int8_gemv_fused_epilogue(dev, ws):
+    N, K = 1152, 4096
+    case, x, W, sc = _w8_case(N, K, 7600)
+    g = torch.Generator().manual_seed(9)
+    bias, res = torch.randn(N, generator=g).half(), torch.randn(1, N, generator=g).half()
+    ref = oracle.epilogue(oracle.gemm_w8a16_nk(x.numpy(), W.numpy(), sc.numpy()), bias.numpy(), res.numpy(), capi.ACT["silu"])
+    xd, Wd, sd, bd, rd = x.to(dev), W.to(dev), sc.to(dev), bias.to(dev), res.to(dev)
+    C = torch.full((1, N), float("nan"), dtype=torch.half, device=dev)
+    ep = capi.Epilogue(bd.data_ptr(), rd.data_ptr(), capi.ACT["silu"])
+    st = L.fg_gemm_fused(capi.FG_OP_W8A16_NK, xd.data_ptr(), Wd.data_ptr(), sd.data_ptr(), C.data_ptr(), 1, N, K, ctypes.byref(ep),
+                         ws.ptr, ws.bytes, gu.stream())
+    assert st == capi.FG_OK, capi.status_str(st)
+    torch.cuda.synchronize()
+    oracle.check_tolerance(C.cpu().numpy(), ref, "w8 gemv fused")
+
+
+def test_int8_rows_too_short_or_too_many_tokens_stay_tiled():
+    for (M, N, K) in [(2, 4096, 4096), (8, 28672, 8192), (1, 256, 1024), (1, 128, 65536)]:
+        assert capi.plan(wl.OP_W8, M, N, K, 148, 232448).math != 4

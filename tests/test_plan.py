@@ -69,9 +69,10 @@ SHAPES = [(1, 1, 8192, 8192), (1, 2, 8192, 8192), (1, 2, 3072, 12288), (1, 1, 12
 
 def check_gemv_plan(p, M, N, K):
     """Row-split GEMV kernel (math 4): every weight row is streamed exactly once, by one CTA."""
-    assert p.op == 1 and 1 <= M <= 2 and p.m_tile == M and p.passes == 1
+    assert (p.op == 1 and 1 <= M <= 2) or (p.op == 2 and M == 1), "fp16 rows for one or two tokens, int8 rows for one"
+    assert p.m_tile == M and p.passes == 1
     assert p.rows_per_stage in (1, 2, 4, 8) and p.rows_per_stage * M <= 8
-    assert p.rows_per_stage * K * 2 <= 65536 and p.k_per_stage == K and p.k_blocks == 1
+    assert p.rows_per_stage * K * (1 if p.op == 2 else 2) <= 65536 and p.k_per_stage == K and p.k_blocks == 1
     assert 3 <= p.stages <= 24 and 1 <= p.consumer_warps <= 12 and p.stages % p.consumer_warps == 0
     assert 1 <= p.grid <= 148 and p.smem_bytes <= 232448
     assert p.static_rows % p.rows_per_stage == 0 and p.static_rows * p.grid <= N
