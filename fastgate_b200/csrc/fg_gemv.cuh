@@ -1,6 +1,7 @@
 // Row-split GEMV for one or two token rows, CUDA-core math, sm_100a.
 //
 //   C[m, n] = sum_k x[m, k] * W[n, k]        m < M <= 2,  W fp16
+//   C[0, n] = scale[n] * sum_k x[0, k] * W8[n, k]         W8 int8, one token row
 //
 // With so few token rows the tensor cores buy nothing; what costs time is everything around the
 // stream: a reduction between CTAs, a tail of dependent memory round trips, SMs that finish at
@@ -28,8 +29,9 @@
 //    different stages at the same time, and the per-stage overhead of a thread is amortised over
 //    hundreds of weights.  The order of every sum is fixed.
 //
-// Replaces gemv_fp16 (backend/cuda/hk/fastgemv.cuh:503-562) and
-// gemv_fp16_bs2 (backend/cuda/czn/fastgemm.cuh:302-392) of the reference, and serves
+// Replaces gemv_fp16 (backend/cuda/hk/fastgemv.cuh:503-562),
+// gemv_fp16_bs2 (backend/cuda/czn/fastgemm.cuh:302-392) and gemv_quantized_int8
+// (backend/cuda/hk/fastgemv.cuh:316-389) of the reference, and serves
 // edgemm_m8n128k64x4_bt and its aliases when they are called with at most four rows.
 #pragma once
 #include "fg_kernels.cuh"

@@ -80,8 +80,9 @@ typedef struct fg_plan_t {
                         ceil(M / 16) otherwise                                  */
   int math;          /* 0 = mma.sync tiles, accumulators in registers; 2 = tcgen05.mma, accumulator in
                         tensor memory; 4 = row-split GEMV kernel (mixed-precision FMA, whole weight
-                        rows per CTA, no reduction between CTAs; then m_tile = M <= 2, k_per_stage = K,
-                        k_blocks = 1); 1 and 3 reserved                                   */
+                        rows per CTA, no reduction between CTAs; fp16 NxK weights with M <= 2 or int8
+                        weights with M = 1; then m_tile = M, k_per_stage = K, k_blocks = 1); 1 and 3
+                        reserved                                                          */
   int pdl;           /* 1 = programmatic dependent launch: the kernel may start, and prefetch
                         weight tiles, while the previous kernel of the stream drains; it reads
                         activations and writes nothing before that kernel has completed       */
