@@ -103,7 +103,9 @@ __device__ __forceinline__ void fma_i8x4_f32(float& acc0, float& acc1, uint32_t 
 }
 
 // The same stage for int8 weights (one token row): lane l takes the 16-byte pieces l, l + 32, ... of
-// every row, sixteen k each, against 32 bytes of x.
+// every row, sixteen k each, against 32 bytes of x.  x sits in shared memory as two halves: the
+// first eight activations of every group of sixteen, then the second eight, so that each of the two
+// loads is 16 bytes per lane at a lane stride of 16 bytes (no bank conflicts).
 template <int RB>
 __device__ __forceinline__ void gemv_stage_i8(uint32_t wbase, uint32_t xbase, int K, int nrows, int lane,
                                               float (&out)[kGemvMaxOut]) {
@@ -115,8 +117,8 @@ __device__ __forceinline__ void gemv_stage_i8(uint32_t wbase, uint32_t xbase, in
 #pragma unroll 4
   for (int i = lane; i < pieces; i += 32) {
     uint32_t xv[8];
-    lds_v4(xbase + i * 32, xv[0], xv[1], xv[2], xv[3]);
-    lds_v4(xbase + i * 32 + 16, xv[4], xv[5], xv[6], xv[7]);
+    lds_v4(xbase + i * 16, xv[0], xv[1], xv[2], xv[3]);
+    lds_v4(xbase + row_bytes + i * 16, xv[4], xv[5], xv[6], xv[7]);
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
       if (RB > 1 && r >= nrows) break;
@@ -317,8 +319,14 @@ __global__ void __launch_bounds__((kGemvMaxWarps + 1) * 32, 1) fg_gemv_kernel(co
       const uint4* src = reinterpret_cast<const uint4*>(p.x);
       uint4* dst = reinterpret_cast<uint4*>(smem_gen);
       const int n16 = (M * K) >> 3;
-      if (!dead)
-        for (int i = threadIdx.x; i < n16; i += nt) dst[i] = __ldg(src + i);
+      if (!dead) {
+        if constexpr (WB == 1) {
+          // int8 weights: even 16-byte chunks first, then the odd ones (see gemv_stage_i8)
+          for (int i = threadIdx.x; i < n16; i += nt) dst[(i & 1) * (K >> 4) + (i >> 1)] = __ldg(src + i);
+        } else {
+          for (int i = threadIdx.x; i < n16; i += nt) dst[i] = __ldg(src + i);
+        }
+      }
       named_bar_sync(1, nt);
       if (trace && threadIdx.x == 0) trace[10] = globaltimer_ns();  // x is in shared memory
     }
