@@ -50,7 +50,7 @@ N_WEIGHT_COPIES = 4
 N_BATCHES = 5
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of the named kernel
 # on an 8192 x 8192 weight (see the profile summaries that ship with the repository)
-NCU_TRAFFIC = {"kernel": "fg::fg_umma_kernel<1,16>", "bytes_per_launch": 138.3e6}
+NCU_TRAFFIC = {"kernel": "fg::fg_umma_kernel<1,16>", "bytes_per_launch": 137.8e6}
 METRIC = "effective HBM GB/s of M<=16 fp16 GEMM-GEMV (edgemm_m8n128k64x4_bt, K=N=8192)"
 WORKLOAD = "bt_sweep: edgemm_m8n128k64x4_bt, M in {1,2,4,8,16}, K=N=8192 per GPU, weight NxK fp16"
 
@@ -813,10 +813,10 @@ def run_ours(args):
     roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
             "traffic": NCU_TRAFFIC["bytes_per_launch"], "traffic_kernel": NCU_TRAFFIC["kernel"],
-            "kernel": "fg::fg_umma_kernel<1,16> (M = 4, 8, 16) and fg::fg_gemv_kernel<M> (M = 1, 2): average over the step's five launches",
+            "kernel": "fg::fg_umma_kernel<1,16> (M = 2, 4, 8, 16) and fg::fg_gemv_kernel<1,2> (M = 1): average over the step's five launches",
             "algorithmic_bytes_per_launch": avg_bytes}
     if per_call:
-        umma = [c for c in cases if c.M > 2]
+        umma = [c for c in cases if "fg_umma" in per_call[f"M{c.M}"]["kernel"]]
         t_umma = sum(per_call[f"M{c.M}"]["us"] for c in umma) / len(umma)
         b_umma = sum(c.algorithmic_bytes for c in umma) / len(umma)
         roof["dominant_kernel"] = {"kernel": "fg::fg_umma_kernel<1,16>", "us_per_launch": t_umma, "achieved": b_umma / t_umma / 1e3,
@@ -861,7 +861,7 @@ def fg_plan_name(M: int) -> str:
     from fastgate_b200 import capi
 
     p = capi.plan(capi.FG_OP_F16_NK, M, 8192, 8192)
-    return {4: f"fg::fg_gemv_kernel<{M}>", 2: f"fg::fg_umma_kernel<1,{p.m_tile}>", 0: f"fg::fg_streamk_kernel<1,{p.m_tile}>"}[p.math]
+    return {4: f"fg::fg_gemv_kernel<{M},2>", 2: f"fg::fg_umma_kernel<1,{p.m_tile}>", 0: f"fg::fg_streamk_kernel<1,{p.m_tile}>"}[p.math]
 
 
 def run_other_workload(args):
