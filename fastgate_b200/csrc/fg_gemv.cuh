@@ -9,7 +9,7 @@
 // summed inside one CTA in a fixed order and nothing is ever exchanged between CTAs.
 //
 //  * One persistent CTA per SM.  Rows of an NxK weight are contiguous, so a ring stage is one
-//    untiled bulk copy (cp.async.bulk, no cluster multicast) of 1-8 whole rows, about 32 KB.
+//    untiled bulk copy (cp.async.bulk, no cluster multicast) of 1-8 whole rows, about 16 KB.
 //  * Each CTA first streams a fixed share of rows (known without asking anybody, so the first
 //    ring-full is requested before griddepcontrol.wait) and then takes blocks of rows from a
 //    counter in the workspace until none are left; the result does not depend on who computed a
@@ -32,7 +32,7 @@
 // Replaces gemv_fp16 (backend/cuda/hk/fastgemv.cuh:503-562),
 // gemv_fp16_bs2 (backend/cuda/czn/fastgemm.cuh:302-392) and gemv_quantized_int8
 // (backend/cuda/hk/fastgemv.cuh:316-389) of the reference, and serves
-// edgemm_m8n128k64x4_bt and its aliases when they are called with at most four rows.
+// edgemm_m8n128k64x4_bt and its aliases when they are called with one row (two rows for weights of up to 48 Mi elements).
 #pragma once
 #include "fg_kernels.cuh"
 
@@ -121,7 +121,6 @@ __device__ __forceinline__ void gemv_stage_i8(uint32_t wbase, uint32_t xbase, in
     lds_v4(xbase + row_bytes + i * 16, xv[4], xv[5], xv[6], xv[7]);
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
-      if (RB > 1 && r >= nrows) break;
       uint32_t wv[4];
       lds_v4(wbase + r * row_bytes + i * 16, wv[0], wv[1], wv[2], wv[3]);
       fma_i8x4_f32(acc[r][0], acc[r][1], wv[0], xv[0], xv[1]);
@@ -152,9 +151,10 @@ __device__ __forceinline__ void gemv_stage(uint32_t wbase, uint32_t xbase, int K
     uint32_t xv[M][4];
 #pragma unroll
     for (int m = 0; m < M; ++m) lds_v4(xbase + (static_cast<uint32_t>(m) * K + i * 8) * 2, xv[m][0], xv[m][1], xv[m][2], xv[m][3]);
+    // all RB rows of the slot, also where the stage holds fewer (the last block of a share): what the
+    // slot's other rows hold is stale but readable, and their sums are never stored
 #pragma unroll
     for (int r = 0; r < RB; ++r) {
-      if (RB > 1 && r >= nrows) break;
       uint32_t wv[4];
       lds_v4(wbase + r * row_bytes + i * 16, wv[0], wv[1], wv[2], wv[3]);
 #pragma unroll
@@ -381,7 +381,7 @@ __global__ void __launch_bounds__((kGemvMaxWarps + 1) * 32, 1) fg_gemv_kernel(co
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         const int r = i / M, m = i - r * M;
-        if (lane == m * nrows + r) mine = v;
+        if (r < nrows && lane == m * nrows + r) mine = v;
       }
       if (lane < nrows * M) {
         const int m = lane / nrows, r = lane - m * nrows;

@@ -42,6 +42,8 @@ static inline int fg_smem_bytes(int op, int m_tile, int chunks, int stages, int 
 #define FG_GEMV_M2_MAX_ELEMS (48LL << 20) /* two rows: only up to this many weights (96 MB) */
 #define FG_GEMV_MAX_OUT 8                /* rows per stage x token rows */
 #define FG_GEMV_MAX_WARPS 12             /* consumer warps; each owns every warps-th stage */
+#define FG_GEMV_PREF_WARPS_MIN 5         /* one row of fp16 weights: the planner looks for a ring depth that this many ... */
+#define FG_GEMV_PREF_WARPS_MAX 9         /* ... to this many warps divide */
 #define FG_GEMV_MIN_K 1024
 #define FG_GEMV_STAGE_TARGET_BYTES 16384 /* as many rows per stage as fit in this */
 #define FG_GEMV_MAX_STAGE_BYTES 65536    /* a stage holds at least one whole row */

@@ -79,6 +79,27 @@ static int plan_gemv(int op, int M, int N, int K, int sm_count, int smem_optin_b
       best_w = fg_gemv_warps(s2);
       best_s = s2;
     }
+  if (op == FG_OP_F16_NK && M == 1) {
+    // One token row of fp16 weights: five to nine warps with two or three ring slots each beat twelve
+    // warps with one slot each wherever the ring is deep enough to choose (measured on B200, us per call,
+    // twelve warps against this rule: 8192 x 8192 22.7 / 21.7, 11008 x 4096 15.4 / 13.9, 4096 x 4096
+    // 8.9 / 8.3, 8192 x 7168 20.0 / 18.5, 8192 x 2048 8.4 / 7.8; 8192 x 6144 and 8192 x 5120 are unchanged
+    // at 16 slots / 8 warps and 21 / 7).  A warp multiplies about 12 GB/s, an SM receives 47 GB/s:
+    // more warps than that needs only add contention for the issue slots and shared memory.
+    for (int s2 = fit; s2 >= 3 && s2 >= fit - 3; --s2) {
+      int w = 0;
+      for (int c = FG_GEMV_PREF_WARPS_MAX; c >= FG_GEMV_PREF_WARPS_MIN; --c)
+        if (s2 % c == 0) {
+          w = c;
+          break;
+        }
+      if (w != 0) {
+        best_s = s2;
+        best_w = w;
+        break;
+      }
+    }
+  }
   p.stages = best_s;
   p.consumer_warps = best_w;
   const int blocks = (N + rows - 1) / rows;
