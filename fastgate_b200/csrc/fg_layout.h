@@ -76,6 +76,8 @@ extern "C" int fg_plan_tiled(int op, int M, int N, int K, int sm_count, int smem
 #define FG_UMMA_Q_STAGING_BYTES 98304 /* three 32 KB buffers */
 static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages);
 
+/* fp16 weights up to this size get a grid of tiles x s CTAs (every CTA one segment of one tile) */
+#define FG_ALIGNED_GRID_MAX_BYTES (80LL << 20)
 /* tcgen05 variant: ring + barriers only (the accumulators live in tensor memory) */
 static inline int fg_umma_smem_bytes_mt(int op, int m_tile, int chunks, int stages) {
   return 1024 + stages * (chunks * fg_chunk_bytes(op, m_tile) + 16) + 64;
