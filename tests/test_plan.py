@@ -131,6 +131,32 @@ def test_streamk_split(tiles, k_blocks, grid):
     simulate(tiles, k_blocks, grid)
 
 
+@pytest.mark.parametrize("op,M,N,K,grid", [(1, 16, 4096, 4096, 128), (1, 16, 3072, 3072, 96), (0, 8, 4096, 4096, 128), (0, 8, 3072, 3072, 96),
+                                            (1, 4, 2048, 8192, 128), (1, 16, 9216, 3072, 144), (1, 16, 3072, 12288, 144),
+                                            (0, 8, 1152, 3072, 72), (1, 16, 4096, 2048, 128)])
+def test_small_problems_get_tile_aligned_grids(op, M, N, K, grid):
+    """Up to 80 MB of fp16 weights: tiles x s CTAs, s a divisor of the stages per tile, so that every CTA
+    owns one segment of one tile and every tile is reduced over exactly s contributors."""
+    p = capi.plan(op, M, N, K, **B200)
+    assert p.math in (0, 2) and p.grid == grid, p.as_dict()
+    s = p.grid // p.tiles
+    assert p.grid == p.tiles * s and p.k_blocks % s == 0 and s >= 2
+    contrib = simulate(p.tiles, p.k_blocks, p.grid)
+    total = p.tiles * p.k_blocks
+    for t in range(p.tiles):
+        assert contrib[t] == [(c, 0) for c in range(t * s, (t + 1) * s)]
+    for c in range(p.grid):
+        assert _range_begin(c + 1, total, p.grid) - _range_begin(c, total, p.grid) == p.k_blocks // s
+    assert capi.lib.fg_plan_validate(ctypes.byref(p), N, K, 232448) == capi.FG_OK
+
+
+def test_large_or_awkward_problems_keep_all_sms():
+    for (op, M, N, K) in [(1, 16, 8192, 8192), (1, 16, 12288, 3072), (0, 8, 8192, 8192), (1, 16, 11008, 4096), (2, 8, 4096, 4096),
+                          (1, 16, 1152, 3072)]:
+        p = capi.plan(op, M, N, K, **B200)
+        assert p.grid == min(148, p.tiles * p.k_blocks), p.as_dict()
+
+
 def test_plan_rejects_bad_problems():
     p = capi.Plan()
     L = capi.lib
