@@ -78,6 +78,8 @@ static inline int fg_umma_q_smem_bytes(int op, int chunks, int stages);
 
 /* fp16 weights up to this size get a grid of tiles x s CTAs (every CTA one segment of one tile) */
 #define FG_ALIGNED_GRID_MAX_BYTES (80LL << 20)
+/* ... and what counts as a small problem there (smaller grids allowed; KxN weights up to 8 rows stay on the mma.sync kernel) */
+#define FG_ALIGNED_GRID_SMALL_BYTES (40LL << 20)
 /* tcgen05 variant: ring + barriers only (the accumulators live in tensor memory) */
 static inline int fg_umma_smem_bytes_mt(int op, int m_tile, int chunks, int stages) {
   return 1024 + stages * (chunks * fg_chunk_bytes(op, m_tile) + 16) + 64;

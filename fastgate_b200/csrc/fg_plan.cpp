@@ -119,7 +119,9 @@ static int plan_gemv(int op, int M, int N, int K, int sm_count, int smem_optin_b
 // 12.6 / 11.4, 3072 x 3072 10.8 / 8.6, 1152 x 3072 11.3 / 8.8.  Above about 80 MB of weights a CTA streams so
 // many stages that the balance of bytes matters more (8192 x 8192 loses 0.9 us on 128 CTAs).
 // Preference: the largest such grid that leaves a CTA at least 192 KB of weights, else at least 96 KB;
-// never fewer than 48 % of the SMs.  Returns 0 when nothing qualifies.
+// never fewer than 48 % of the SMs, and 60 % above 40 MB of weights (5120 x 5120 on 80 CTAs and 7168 x 4096
+// on 112 are level with all SMs or slower; 6144 x 4096 on 96, 4096 x 8192 on 128 and 6144 x 6144 on 144
+// gain 3-10 %).  Returns 0 when nothing qualifies.
 static int aligned_grid(int tiles, int k_blocks, long long stage_bytes, int sm_count) {
   const long long weight_bytes = static_cast<long long>(tiles) * k_blocks * stage_bytes;
   if (weight_bytes > FG_ALIGNED_GRID_MAX_BYTES) return 0;
@@ -129,7 +131,7 @@ static int aligned_grid(int tiles, int k_blocks, long long stage_bytes, int sm_c
     for (int s = 2; s <= k_blocks; ++s) {
       if (k_blocks % s) continue;
       const long long g = static_cast<long long>(tiles) * s;
-      if (g > limit || g * 100 < 48LL * sm_count) continue;
+      if (g > limit || g * 100 < (weight_bytes > FG_ALIGNED_GRID_SMALL_BYTES ? 60LL : 48LL) * sm_count) continue;
       if ((k_blocks / s) * stage_bytes < per_cta) continue;
       if (g > best) best = static_cast<int>(g);
     }
@@ -172,7 +174,11 @@ static int plan_impl(int op, int M, int N, int K, int sm_count, int smem_optin_b
   p.tiles = N / 128;
 
   const int chunk_k = fg_chunk_k(op);
-  if (!quantized && (p.m_tile >= 16 || op == FG_OP_F16_NK)) {
+  // KxN weights up to 8 rows: the mma.sync kernel up to 40 MB of weights (measured at M = 8: 3072 x 3072 8.6 us against
+  // 9.6 for the tcgen05 kernel, 4096 x 2048 8.7 / 9.0, 4096 x 4096 11.4 / 11.5), the tcgen05 kernel above (5120 x 5120
+  // 17.7 / 14.9, 8192 x 4096 16.8 / 15.4, 11008 x 4096 20.0 / 18.4, 8192 x 8192 25.8 / 24.8)
+  const bool kn_large = (op == FG_OP_F16_KN && static_cast<long long>(N) * K * 2 > FG_ALIGNED_GRID_SMALL_BYTES);
+  if (!quantized && (p.m_tile >= 16 || op == FG_OP_F16_NK || kn_large)) {
     // NxK fp16 weights at every M, KxN above 8 token rows (measured: with 64 KB stages the tcgen05
     // kernel is 1.5-5 % faster than the mma.sync one for NxK at M = 1 and 8 on 8192^2, 11008 x 4096,
     // 4096 x 11008 and 3072^2, and 3 % slower for KxN at 4096^2): the tcgen05 kernel (accumulator in tensor memory,

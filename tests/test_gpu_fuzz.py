@@ -46,3 +46,12 @@ def test_random_shapes(case, dev, ws):
     p = capi.plan(case.op, case.M, case.N, case.K, 148, 232448)
     assert p.math in (0, 2, 4)
     run_case(case, dev, ws)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(8192, 4096), (5120, 5120), (4096, 8192)])
+def test_large_kn_weights_with_few_rows_run_the_tcgen05_kernel(M, N, K, dev, ws):
+    """KxN weights above 40 MB leave the mma.sync kernel also for M <= 8 (rows beyond M are zero-filled)."""
+    assert capi.plan(wl.OP_KN, M, N, K, 148, 232448).math == 2
+    assert capi.plan(wl.OP_KN, M, 4096, 4096, 148, 232448).math == 0
+    run_case(wl.Case(f"kn_large_M{M}_N{N}_K{K}", wl.OP_KN, M, N, K, 13000 + M + N), dev, ws)

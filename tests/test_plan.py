@@ -114,8 +114,8 @@ def test_plan_invariants(op, M, N, K):
     else:
         assert p.math == 2 and p.m_tile >= 16, "tcgen05 kernels: accumulator in tensor memory"
         assert p.stages >= 3 or p.k_per_stage == CHUNK_K[op]
-    # NxK fp16 weights always take the tcgen05 kernel, everything else above 8 token rows
-    assert (p.math == 2) == (M > 8 or op == 1)
+    # NxK fp16 weights always take the tcgen05 kernel, KxN ones above 40 MB, everything else above 8 token rows
+    assert (p.math == 2) == (M > 8 or op == 1 or (op == 0 and N * K * 2 > 40 << 20))
     assert p.smem_bytes <= 232448
     rows = 64 if (p.math == 2 and op in (0, 1)) else 16
     assert p.passes == -(-M // rows)
@@ -169,7 +169,7 @@ def test_plan_rejects_bad_problems():
 
 def test_validate_catches_edited_plans():
     L = capi.lib
-    good = capi.plan(0, 8, 8192, 8192, **B200)  # KxN weights at 8 rows: the mma.sync kernel
+    good = capi.plan(0, 8, 4096, 4096, **B200)  # KxN weights at 8 rows, up to 40 MB: the mma.sync kernel
     assert good.math == 0
 
     def edited(**kw):
@@ -177,7 +177,7 @@ def test_validate_catches_edited_plans():
         ctypes.memmove(ctypes.byref(q), ctypes.byref(good), ctypes.sizeof(q))
         for k, v in kw.items():
             setattr(q, k, v)
-        return L.fg_plan_validate(ctypes.byref(q), 8192, 8192, 232448)
+        return L.fg_plan_validate(ctypes.byref(q), 4096, 4096, 232448)
 
     assert edited() == capi.FG_OK
     assert edited(stages=good.stages + 1) == capi.FG_ERR_PLAN      # smem no longer matches / not a multiple
