@@ -436,9 +436,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) fg_umma_chain_kernel(const CP
                     for (int q = 0; q < 4; ++q)
                       o[q] = act_fn<ACT>(o[q] + __half2float(bias4[q])) + __half2float(res4[i][q]);
                   }
-                  __half2* dst = reinterpret_cast<__half2*>(Cb + static_cast<size_t>(m) * ldc + n0);
-                  dst[0] = __floats2half2_rn(o[0], o[1]);
-                  dst[1] = __floats2half2_rn(o[2], o[3]);
+                  // one 8-byte store per row and lane: the number of stores, not their bytes, is what the
+                  // layers waiting for this tile feel
+                  const __half2 lo = __floats2half2_rn(o[0], o[1]), hi = __floats2half2_rn(o[2], o[3]);
+                  uint2 w;
+                  w.x = *reinterpret_cast<const uint32_t*>(&lo);
+                  w.y = *reinterpret_cast<const uint32_t*>(&hi);
+                  *reinterpret_cast<uint2*>(Cb + static_cast<size_t>(m) * ldc + n0) = w;
                 }
               }
             });

@@ -115,6 +115,24 @@ __device__ __forceinline__ void group_store2(const GParams& g, const GroupEntry*
     for (int q = 0; q < g.world; ++q) *reinterpret_cast<__half2*>(e->peer_C[q] + off) = h;
   }
 }
+// Four adjacent outputs (n a multiple of 4) as one 8-byte store where the destination is plain memory.
+__device__ __forceinline__ void group_store4(const GParams& g, const GroupEntry* e, int m, int n, float4 v) {
+  if (g.world != 0 && g.mc_flag != nullptr) {
+    group_store2(g, e, m, n, make_float2(v.x, v.y));
+    group_store2(g, e, m, n + 2, make_float2(v.z, v.w));
+    return;
+  }
+  const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+  uint2 w;
+  w.x = *reinterpret_cast<const uint32_t*>(&lo);
+  w.y = *reinterpret_cast<const uint32_t*>(&hi);
+  if (g.world == 0) {
+    *reinterpret_cast<uint2*>(e->C + static_cast<size_t>(m) * e->N + n) = w;
+  } else {
+    const size_t off = static_cast<size_t>(m) * e->ldc + e->col0 + n;
+    for (int q = 0; q < g.world; ++q) *reinterpret_cast<uint2*>(e->peer_C[q] + off) = w;
+  }
+}
 __device__ __forceinline__ void group_signal(const GParams& g) {
   if (g.mc_flag != nullptr) {
     multimem_red_release_add_u64(g.mc_flag + g.rank, 1ull);
@@ -344,10 +362,7 @@ __global__ void __launch_bounds__(kUmmaGroupThreads, 1) fg_umma_group_kernel(con
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               const int m = m0 + i;
-              if (m < M) {
-                group_store2(g, c.e, m, n0, make_float2(sum[i].x, sum[i].y));
-                group_store2(g, c.e, m, n0 + 2, make_float2(sum[i].z, sum[i].w));
-              }
+              if (m < M) group_store4(g, c.e, m, n0, sum[i]);
             }
           }
         }
