@@ -699,6 +699,9 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
         if (ok) {
           __threadfence();
           prev = atomicAdd(p.tickets + tile, 1u);
+          // the last contributor: acquire the other CTAs' partial tiles for the whole team (the barrier
+          // below carries this thread's fence to the other warps; one fence instead of one per thread)
+          if (prev == c_last - c_first) fence_acq_rel_gpu();
         } else {
           atomicExch(p.status, kStatusTimeout);
         }
@@ -711,7 +714,6 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
         // Warp w takes rows 4w..4w+3 of the tile: lanes 0-15 rows 4w and 4w + 2, lanes 16-31 rows 4w + 1 and
         // 4w + 3, eight columns per lane, so a row leaves as sixteen 16-byte stores of one instruction.
         // Contributors are added in CTA order, four at a time (sixteen 16-byte loads in flight per lane).
-        __threadfence();
         const int hw = lane >> 4, cl = lane & 15;
         const int n0 = tile * kTileN + 8 * cl;
 #pragma unroll 1
@@ -761,7 +763,6 @@ __device__ __forceinline__ void run_finisher(const KParams& p, const CtaRange& r
         }
       } else if (prev == c_last - c_first) {
         // SiLU gate: lanes 0-15 hold gate columns 4l..4l+3 of the tile, lanes 16-31 the matching up columns
-        __threadfence();
 #pragma unroll 1
         for (int m0 = 4 * fin_warp; m0 < MT && m0 < p.M; m0 += 4 * FW) {
           float4 sum[4];
