@@ -28,6 +28,10 @@
 //    residual and rounds once to fp16.  No barrier and no reduction spans the warps: they work on
 //    different stages at the same time, and the per-stage overhead of a thread is amortised over
 //    hundreds of weights.  The order of every sum is fixed.
+//  * How many warps: a warp multiplies about 12 GB/s of fp16 weights for one token row and an SM
+//    receives 47 GB/s, so the planner gives one row of fp16 weights five to nine warps that own two
+//    or three ring slots each (a warp multiplies one slot while its others refill); two token rows
+//    and int8 weights, which do two and four times the work per byte, get up to twelve.
 //
 // Replaces gemv_fp16 (backend/cuda/hk/fastgemv.cuh:503-562),
 // gemv_fp16_bs2 (backend/cuda/czn/fastgemm.cuh:302-392) and gemv_quantized_int8
