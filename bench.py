@@ -50,7 +50,7 @@ N_WEIGHT_COPIES = 4
 N_BATCHES = 5
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of the named kernel
 # on an 8192 x 8192 weight (see the profile summaries that ship with the repository)
-NCU_TRAFFIC = {"kernel": "fg::fg_umma_kernel<1,16>", "bytes_per_launch": 137.8e6}
+NCU_TRAFFIC = {"kernel": "fg::fg_umma_kernel<1,16>", "bytes_per_launch": 138.0e6}
 METRIC = "effective HBM GB/s of M<=16 fp16 GEMM-GEMV (edgemm_m8n128k64x4_bt, K=N=8192)"
 WORKLOAD = "bt_sweep: edgemm_m8n128k64x4_bt, M in {1,2,4,8,16}, K=N=8192 per GPU, weight NxK fp16"
 
