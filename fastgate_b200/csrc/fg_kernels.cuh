@@ -462,11 +462,7 @@ __device__ __forceinline__ void store_out8(const KParams& p, int m, int n, float
     // eight columns never straddle a split (split1 and split2 are multiples of 8) and start 16-byte aligned
     *reinterpret_cast<uint4*>(out_ptr(p, m, n)) = w;
   } else if (p.mc_C != nullptr) {
-    __half* dst = p.mc_C + static_cast<size_t>(m) * p.ldc + p.col0 + n;
-    multimem_st_b32(dst, w.x);
-    multimem_st_b32(dst + 2, w.y);
-    multimem_st_b32(dst + 4, w.z);
-    multimem_st_b32(dst + 6, w.w);
+    multimem_st_v4_f16x2(p.mc_C + static_cast<size_t>(m) * p.ldc + p.col0 + n, w.x, w.y, w.z, w.w);
   } else {
     const size_t off = static_cast<size_t>(m) * p.ldc + p.col0 + n;
     for (int q = 0; q < p.world; ++q) *reinterpret_cast<uint4*>(p.peer_C[q] + off) = w;

@@ -61,6 +61,15 @@ __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity
 __device__ __forceinline__ void multimem_st_b32(void* mc_ptr, uint32_t v) {
   asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
 }
+// Eight fp16 values (16 bytes, 16-byte aligned) as one multicast store.
+__device__ __forceinline__ void multimem_st_v4_f16x2(void* mc_ptr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+// Four fp16 values (8 bytes, 8-byte aligned) as one multicast store.
+__device__ __forceinline__ void multimem_st_v2_f16x2(void* mc_ptr, uint32_t a, uint32_t b) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f16x2 [%0], {%1,%2};" ::"l"(mc_ptr), "r"(a), "r"(b) : "memory");
+}
 __device__ __forceinline__ void multimem_red_release_add_u64(unsigned long long* mc_ptr, unsigned long long v) {
   asm volatile("multimem.red.release.sys.global.add.u64 [%0], %1;" ::"l"(mc_ptr), "l"(v) : "memory");
 }

@@ -117,16 +117,13 @@ __device__ __forceinline__ void group_store2(const GParams& g, const GroupEntry*
 }
 // Four adjacent outputs (n a multiple of 4) as one 8-byte store where the destination is plain memory.
 __device__ __forceinline__ void group_store4(const GParams& g, const GroupEntry* e, int m, int n, float4 v) {
-  if (g.world != 0 && g.mc_flag != nullptr) {
-    group_store2(g, e, m, n, make_float2(v.x, v.y));
-    group_store2(g, e, m, n + 2, make_float2(v.z, v.w));
-    return;
-  }
   const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
   uint2 w;
   w.x = *reinterpret_cast<const uint32_t*>(&lo);
   w.y = *reinterpret_cast<const uint32_t*>(&hi);
-  if (g.world == 0) {
+  if (g.world != 0 && g.mc_flag != nullptr) {
+    multimem_st_v2_f16x2(e->mc_C + static_cast<size_t>(m) * e->ldc + e->col0 + n, w.x, w.y);
+  } else if (g.world == 0) {
     *reinterpret_cast<uint2*>(e->C + static_cast<size_t>(m) * e->N + n) = w;
   } else {
     const size_t off = static_cast<size_t>(m) * e->ldc + e->col0 + n;

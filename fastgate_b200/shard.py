@@ -14,7 +14,7 @@ Every shard keeps the kernels' contract (N/g % 128 == 0).  The gather delivers
 128-column tile directly into the full ``C[M, N]`` of every rank through NVLink peer
 mappings (torch symmetric memory) and bumps each rank's arrival counter; a one-thread wait
 kernel then holds the stream until all ranks' tiles have landed.  No NCCL call, no
-``[g,M,N/g] -> [M,N]`` copy.  Peer stores and atomics over NVLink mappings, or, from 4 ranks on
+``[g,M,N/g] -> [M,N]`` copy.  Peer stores and atomics over NVLink mappings, or, where the fabric offers multicast mappings
 (``FASTGATE_MULTIMEM=0|1`` overrides), one ``multimem.st`` / ``multimem.red`` per tile that the
 NVSwitch replicates to every rank; never a TMA access to peer memory.  The number of tiles a rank
 expects is kept on the device next to the counters (pushing kernels add to it, waits read it), so a
@@ -70,14 +70,14 @@ class PushBuffers:
             # with both, a tile is pushed by one multimem store / reduction instead of one per rank
             self.mc_out = int(getattr(self._h_out, "multicast_ptr", 0) or 0)
             self.mc_flag = int(getattr(self._h_flag, "multicast_ptr", 0) or 0)
-            # Measured on B200 (DiT stack, one grouped launch per pass, all-gather included): at 2 GPUs
-            # the multicast path is 11 % slower than one store per rank (nothing to save on egress, one
-            # more hop through the switch), at 8 GPUs 23 % faster (34.6 against 28.3 TB/s).  At 4 GPUs it
-            # wins on every leg: 8192 x 8192 sweep, one call per launch, 18.7 against 17.6 TB/s; DiT stack
-            # with a push per linear 2.19 against 2.52 ms per pass; as one grouped launch 24.7 against 24.2 TB/s.
-            # Default: on from 4 ranks; FASTGATE_MULTIMEM=0 / 1 forces it off / on.
+            # Measured on B200 with 16- and 8-byte multicast stores, multicast against one store per rank:
+            # 2 GPUs: 8192 x 8192 sweep, one call per launch, 9.5 against 8.9 TB/s; DiT stack with a push per
+            # linear 2.35 against 2.62 ms per pass; as one grouped launch 13.0 against 12.8 TB/s.  4 GPUs (with
+            # 4-byte multicast stores): 18.7 against 17.6 TB/s, 2.19 against 2.52 ms, 24.7 against 24.2 TB/s.
+            # 8 GPUs (an earlier build): grouped 34.6 against 28.3 TB/s.
+            # Default: on wherever the mappings exist; FASTGATE_MULTIMEM=0 / 1 forces it off / on.
             env = os.environ.get("FASTGATE_MULTIMEM")
-            want = (env == "1") if env in ("0", "1") else self.world >= 4
+            want = (env != "0")
             if not (want and self.mc_out and self.mc_flag):
                 self.mc_out = self.mc_flag = 0
             dist.barrier(group)  # every counter is zero before anyone pushes
